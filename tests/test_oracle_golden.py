@@ -165,11 +165,18 @@ def test_top_p_mask_matches_vllm(golden):
         k2, margin = S.top_p_keep(y[idx], p[i])
         got = np.zeros(V, bool)
         got[idx[k2]] = True
+        # torch's sort orders EQUAL values arbitrarily, so which members of a tie
+        # group straddling the nucleus boundary survive is unpinned upstream: the
+        # kept VALUES must agree, and the kept positions wherever values are unique.
+        def same(mine, ref):
+            assert np.array_equal(np.sort(y[mine]), np.sort(y[ref])), i
+            uniq = np.isin(y, y[mine ^ ref], invert=True)
+            assert (mine[uniq] == ref[uniq]).all(), i
         if margin > 1e-5:
-            assert (got == g["keep_kp"][i]).all(), i
+            same(got, g["keep_kp"][i])
         k3, margin = S.top_p_keep(y, p[i])
         if margin > 1e-5:
-            assert (k3 == g["keep_p"][i]).all(), i
+            same(k3, g["keep_p"][i])
 
 
 def test_merge_winners_rule():
