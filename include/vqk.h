@@ -1,0 +1,196 @@
+/*
+ * vqk.h - C ABI of libvqk.so: quantized lm_head + fused sampler for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host binds instead of the reference plugin's Triton
+ * kernels (project himikk/vllm-quant-kernels).  Every entry point cites the
+ * reference interface it replaces as `path:line` inside that project.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; `stream` is a cudaStream_t passed as void*
+ *     (NULL = the legacy default stream);
+ *   - all data pointers are DEVICE pointers unless a comment says host;
+ *   - every function returns VQK_OK (0) or a negative vqk_status; nothing throws,
+ *     nothing calls exit();
+ *   - work is enqueued on `stream` and the call returns without synchronising;
+ *   - the caller owns every buffer, including the workspace whose size the
+ *     *_workspace_bytes functions report; a vqk_lm_head owns no device memory;
+ *   - there is no CPU fallback: on a device that is not compute capability 10.x
+ *     the compute entry points return VQK_ERR_ARCH.
+ */
+#ifndef VQK_H_
+#define VQK_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VQK_VERSION 100
+
+typedef enum {
+  VQK_OK = 0,
+  VQK_ERR_INVALID = -1,      /* bad argument (null pointer, size, alignment, enum) */
+  VQK_ERR_UNSUPPORTED = -2,  /* valid request this build does not implement (e.g. H % 16 != 0) */
+  VQK_ERR_CUDA = -3,         /* a CUDA runtime call failed; see vqk_last_cuda_error */
+  VQK_ERR_WORKSPACE = -4,    /* workspace missing or too small */
+  VQK_ERR_ARCH = -5,         /* current device is not sm_100 */
+  VQK_ERR_COMM = -6,         /* NCCL not loadable or a collective failed */
+  VQK_ERR_TOO_LARGE = -7     /* size beyond a stated fixed maximum */
+} vqk_status;
+
+/* lm_head modes, in the reference's priority order from lowest to highest
+ * (src/vllm_quant_kernels/_registration.py:57-68). */
+typedef enum {
+  VQK_MODE_W8A16 = 0,  /* int8 rows + fp16 scale   (_quant.py:245-255)  kernels int8_gmv / int8_gemm */
+  VQK_MODE_W8A8 = 1,   /* int8 rows + fp32 scale   (_quant.py:285-292)  kernel  int8_w8a8_gemm */
+  VQK_MODE_FP8 = 2,    /* e4m3 rows + fp16 scale   (_quant.py:306-314)  kernel  fp8_gemm */
+  VQK_MODE_MXFP8 = 3,  /* e4m3 + E8M0 per 32       (_quant.py:34-61)    kernel  mxfp8_gemm */
+  VQK_MODE_MXFP4 = 4   /* E2M1 x2/byte + E8M0/32   (_quant.py:64-105)   kernel  mxfp4_gemm (W4A8) */
+} vqk_mode;
+
+typedef enum { VQK_F16 = 0, VQK_BF16 = 1, VQK_F32 = 2 } vqk_dtype;
+
+int vqk_version(void);
+const char* vqk_strerror(int status);
+/* cudaError_t of the most recent failing CUDA call on this host thread (0 if none). */
+int vqk_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------
+ * Offline weight quantisation.  Replaces the torch code in
+ * QuantizedLogitsProcessor._init_int8_weights / _init_w8a8 / _init_fp8 /
+ * _init_mxfp8 / _init_mxfp4 (src/vllm_quant_kernels/_quant.py:245-380) and
+ * _quantize_to_mxfp8 / _quantize_to_mxfp4 (_quant.py:34-105).  Bit-exact.
+ *   w      [V, H] fp16 or bf16 (or fp32), row stride ldw elements
+ *   q      W8A16/W8A8: int8 [V,H]; FP8/MXFP8: e4m3 bytes [V,H]; MXFP4: uint8 [V,H/2],
+ *          even element in the low nibble
+ *   scales W8A16/FP8: fp16 [V]; W8A8: fp32 [V]; MX: uint8 E8M0 [V, H/32]
+ * ------------------------------------------------------------------------- */
+int vqk_quantize_weight(int mode, const void* w, int w_dtype, int64_t V, int64_t H, int64_t ldw,
+                        void* q, void* scales, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Runtime activation quantisation.  Replaces the torch code inside the
+ * launchers: `x.to(float8_e4m3fn)` (_quant.py:413), `_quantize_to_mxfp8(x)`
+ * (_quant.py:448,495), per-tensor int8 (_quant.py:536-540, without the
+ * `.item()` host sync of :548 - the scale stays on the device).
+ *   xq  W8A16: fp16 [B,H] (dtype conversion only); FP8/MX: e4m3 bytes [B,H]; W8A8: int8 [B,H]
+ *   xs  W8A8: float[2] ([0] = scale, [1] = scratch); MX: uint8 [B, H/32]; else ignored
+ * ------------------------------------------------------------------------- */
+int vqk_quantize_act(int mode, const void* x, int x_dtype, int64_t B, int64_t H, int64_t ldx,
+                     void* xq, void* xs, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Sampling parameters (all arrays on the device, length B).  Semantics follow
+ * _gumbel_block_argmax_kernel (src/vllm_quant_kernels/_sampler_kernels.py:38-120)
+ * with Triton's Philox (`tl.rand(seed, global_vocab_index)`):
+ *   temperature NULL        -> every row is plain argmax (HAS_TEMPERATURE=False)
+ *   temperature[i] < 1e-5   -> row i is greedy
+ *   topk_threshold          -> reference style raw-logit threshold, keep l >= thr[i]
+ *                              (_sampler.py:62-93); overrides top_k
+ *   top_k[i]                -> computed on the device; <= 0 or >= vocab_total disables
+ *   top_p[i]                -> nucleus AFTER temperature and top-k, vLLM semantics
+ *                              (vllm/v1/sample/ops/topk_topp_sampler.py:349-369);
+ *                              >= 1 disables.  Not on the reference's fast path.
+ * Token ids are global: local column + vocab_offset; noise uses the global id, so
+ * the result does not depend on how the vocabulary is sharded.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  const float* temperature;
+  const int32_t* seeds;
+  const int32_t* top_k;
+  const float* top_p;
+  const float* topk_threshold;
+  int64_t vocab_offset; /* global id of local column 0 */
+  int64_t vocab_total;  /* global vocabulary size (== V when not sharded) */
+} vqk_sample_params;
+
+/* Per (rank, row) exchange record of a vocab-sharded step: 16-byte header
+ * {float score; int32 token; int32 n; int32 flags} followed by VQK_RECORD_CAP
+ * candidates {float raw_logit; int32 token}.  n == 0: the header holds the
+ * shard's winner; n > 0: the shard's top-k candidate set. */
+#define VQK_RECORD_CAP 126
+#define VQK_RECORD_BYTES 1024
+#define VQK_RECORD_FLAG_OVERFLOW 1  /* more candidates than VQK_RECORD_CAP */
+#define VQK_RECORD_FLAG_NEEDS_ROW 2 /* row needs a full-row pass (top-p without top-k) */
+
+/* ---------------------------------------------------------------------------
+ * lm_head operator.  Replaces QuantizedLogitsProcessor._quantized_forward and the
+ * five launchers _int8/_w8a8/_fp8/_mxfp8/_mxfp4_forward
+ * (src/vllm_quant_kernels/_quant.py:382-643) plus their Triton kernels
+ * (src/vllm_quant_kernels/_kernels.py:21-84,189-248,299-358,412-477,534-632,701-802).
+ * ------------------------------------------------------------------------- */
+typedef struct vqk_lm_head vqk_lm_head;
+
+/* Describe one vocab shard: quantized rows [V, H] and their scales in the layouts
+ * of vqk_quantize_weight.  Host-side object; holds no device memory. */
+int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
+                       vqk_lm_head** out);
+int vqk_lm_head_destroy(vqk_lm_head* h);
+
+/* Workspace for vqk_lm_head_forward at batch B (sample != 0 if sampling is requested). */
+int64_t vqk_lm_head_workspace_bytes(const vqk_lm_head* h, int64_t B, int sample);
+
+/* logits[b, v] = x[b, :] . dequant(W[v, :]) with the mode's epilogue, rounded to fp16
+ * (_quant.py:409,445,492,533,570), plus bias in fp16 (_quant.py:428-429).
+ *   x        [B, H] fp16 or bf16, row stride ldx
+ *   bias     fp16 [V] or NULL
+ *   logits   fp16 [B, ld_logits] or NULL (not written when NULL)
+ *   sp       NULL -> logits only.  Otherwise the sampler runs on the fp16-rounded
+ *            logits inside the same pass:
+ *              tokens/scores non-NULL -> final int64 token ids / fp32 winning scores
+ *                                        (single shard: vocab_total == V);
+ *              records non-NULL       -> [B] exchange records for a sharded step, to
+ *                                        be all-gathered and given to vqk_sample_finalize.
+ */
+int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, int64_t B, int64_t ldx,
+                        const void* bias, void* logits, int64_t ld_logits,
+                        const vqk_sample_params* sp, int64_t* tokens, float* scores, void* records,
+                        void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Measurement aid (no counterpart in the reference): when both are non-NULL cudaEvent_t
+ * handles, every following vqk_lm_head_forward on `h` records `start` right before and
+ * `stop` right after its weight-streaming kernel launch(es) on the call's stream, so a
+ * benchmark can time that kernel in place.  Pass NULLs to switch it off. */
+int vqk_lm_head_set_kernel_events(vqk_lm_head* h, void* start_event, void* stop_event);
+
+/* ---------------------------------------------------------------------------
+ * Stand-alone sampler on materialised logits.  Replaces fused_gumbel_sample
+ * (src/vllm_quant_kernels/_sampler_kernels.py:123-182) and, with top_k / top_p,
+ * the vLLM chain behind FusedSampler.sample (_sampler.py:144-206).
+ *   logits [B, V] fp32 / bf16 / fp16, row stride ld
+ * ------------------------------------------------------------------------- */
+int64_t vqk_sample_workspace_bytes(int64_t B, int64_t V);
+int vqk_sample(const void* logits, int dtype, int64_t B, int64_t V, int64_t ld,
+               const vqk_sample_params* sp, int64_t* tokens, float* scores, void* records,
+               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Merge all-gathered records [G][B] into final tokens; every rank computes the same
+ * answer.  Higher score wins, equal scores go to the lower token id (the first-index
+ * rule of _sampler_kernels.py:116-120,180-181).  Rows whose records carry an overflow
+ * flag get token -1. */
+int vqk_sample_finalize(const void* records, int G, int64_t B, const vqk_sample_params* sp,
+                        int64_t* tokens, float* scores, void* stream);
+
+/* k-th largest raw logit per row; replaces _compute_topk_threshold (_sampler.py:62-93)
+ * without its host sync.  top_k[i] <= 0 or >= V gives -inf for that row. */
+int vqk_topk_threshold(const void* logits, int dtype, int64_t B, int64_t V, int64_t ld,
+                       const int32_t* top_k, float* threshold, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Winner exchange between vocab shards (no counterpart in the reference, which is
+ * single-GPU; the shape follows vLLM's LogitsProcessor.get_top_tokens,
+ * vllm/model_executor/layers/logits_processor.py:106-156).  NCCL is loaded at run
+ * time from the process (the copy PyTorch already loaded) or from libnccl.so.2.
+ * ------------------------------------------------------------------------- */
+typedef struct vqk_comm vqk_comm;
+#define VQK_COMM_ID_BYTES 128
+int vqk_comm_unique_id(void* id_out_host /* VQK_COMM_ID_BYTES */);
+int vqk_comm_create(const void* id_host, int rank, int nranks, vqk_comm** out);
+int vqk_comm_allgather(vqk_comm* c, const void* send, void* recv, int64_t bytes_per_rank, void* stream);
+int vqk_comm_destroy(vqk_comm* c);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VQK_H_ */

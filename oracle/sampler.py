@@ -106,9 +106,12 @@ def top_p_keep(y_kept, p):
     """Upstream top-p on the surviving scaled logits of ONE row.
 
     y_kept : fp32 values (any order).  Returns (keep mask in the same order,
-    boundary margin = min |cumsum - (1 - p)| over the elements).  Equal values
-    are ordered by position (stable sort), so of several equal values the
-    earlier positions are dropped first."""
+    boundary margin = min |cumsum - (1 - p)| over the elements).
+
+    Upstream orders EQUAL values arbitrarily (torch.sort is not stable), so which
+    members of a tie group straddling the nucleus boundary survive is unpinned
+    there.  This build's rule, restated here: every value equal to the smallest
+    surviving value survives too ("ties at the boundary are all kept")."""
     y = np.asarray(y_kept, dtype=F32)
     order = np.argsort(y, kind="stable")
     ys = y[order]
@@ -120,6 +123,7 @@ def top_p_keep(y_kept, p):
     drop[-1] = False
     keep = np.empty_like(drop)
     keep[order] = ~drop
+    keep |= (y == ys[~drop].min())
     margin = float(np.min(np.abs(c[:-1].astype(np.float64) - float(lim)))) if len(c) > 1 else 1.0
     return keep, margin
 

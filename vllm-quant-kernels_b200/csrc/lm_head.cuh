@@ -1,0 +1,91 @@
+// Internal interface between the lm_head kernels, the sampler kernels and the C ABI.
+#pragma once
+
+#include "vqk_common.cuh"
+
+namespace vqk {
+
+struct LmHeadParams {
+  const uint8_t* w;    // quantized rows [V, K] bytes (MXFP4: [V, K/2])
+  const void* wscale;  // fp16 [V] / fp32 [V] / E8M0 [V, K/32]
+  const void* x;       // W8A16: caller's activations [B, ldx] (x_dtype); else quantized bytes [B, K]
+  const void* xscale;  // W8A8: const float* (xs[0]); MX: E8M0 [B, K/32]
+  int x_dtype;
+  int V, K, B;
+  long long ldx;
+  const __half* bias;  // [V] or null
+  __half* logits;      // [B, ld_logits] or null
+  long long ld_logits;
+  int do_sample;
+  SampleDev sp;        // per-row arrays already offset to this launch's first batch row
+  float* slice_max;    // [B][nslices] max raw logit of candidate-path rows
+  float* part_score;   // [B][nslices] per-slice winner of the other rows
+  int* part_token;     // [B][nslices] local token id of that winner
+  int nslices;
+  __half* cand_logits; // [B, ld_cand] fp16 logits of candidate-path rows (scratch or == logits)
+  long long ld_cand;
+};
+
+// lm_head_stream.cu
+size_t stream_smem_bytes(int mode, int K, int NT);
+int stream_max_cols(int mode, int K);  // batch columns one launch can take (0: K too large)
+int launch_lm_head_stream(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
+
+// quantize.cu
+int quantize_act_dispatch(int mode, const void* x, int dt, long long B, long long H, long long ldx, void* xq,
+                          void* xs, cudaStream_t st);
+
+// sampler.cu -------------------------------------------------------------------------------
+struct SelectParams {
+  const void* logits;   // [B, ld] rows in `dtype` (local shard)
+  int dtype;
+  long long ld;
+  int V;                // local columns
+  int B;
+  SampleDev sp;
+  const float* slice_max;   // [B][nslices]
+  const float* part_score;  // [B][nslices]
+  const int* part_token;    // [B][nslices]
+  int nslices;
+  uint8_t* records;     // [B] exchange records (always written)
+  long long* tokens;    // final answers when single shard (may be null)
+  float* scores;
+  int single_shard;     // 1: also resolve candidate rows to a final token here
+  int* rowflag;         // [B] out: 1 if the row still needs the full-row pass
+};
+
+// first pass over materialised logits: per-slice maxima / Gumbel winners (slices of 256 columns)
+int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, float* slice_max,
+                      float* part_score, int* part_token, int nslices, cudaStream_t st);
+inline int slice_pass_nslices(long long V) { return (int)((V + 255) / 256); }
+// cluster-per-row selection: tau from slice maxima, candidate collection, final choice / record
+int launch_select(const SelectParams& p, cudaStream_t st);
+// exact full-row pass for rows flagged in rowflag (top-p without top-k, candidate overflow)
+int launch_fullrow(const SelectParams& p, cudaStream_t st);
+// merge gathered records
+int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, long long* tokens, float* scores,
+                    cudaStream_t st);
+int launch_topk_threshold(const void* logits, int dtype, long long ld, int B, int V, const int32_t* top_k, float* thr,
+                          cudaStream_t st);
+
+inline SampleDev to_dev(const vqk_sample_params* sp) {
+  SampleDev d;
+  d.temperature = sp->temperature;
+  d.seeds = sp->seeds;
+  d.top_k = sp->top_k;
+  d.top_p = sp->top_p;
+  d.thr = sp->topk_threshold;
+  d.vocab_offset = sp->vocab_offset;
+  d.vocab_total = sp->vocab_total;
+  return d;
+}
+inline SampleDev offset_rows(SampleDev d, long long b0) {
+  if (d.temperature) d.temperature += b0;
+  if (d.seeds) d.seeds += b0;
+  if (d.top_k) d.top_k += b0;
+  if (d.top_p) d.top_p += b0;
+  if (d.thr) d.thr += b0;
+  return d;
+}
+
+}  // namespace vqk

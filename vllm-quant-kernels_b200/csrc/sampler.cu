@@ -1,0 +1,587 @@
+// Fused sampler: temperature, top-k, top-p and the Gumbel (exponential-race) argmax.
+//
+// Pass 1 (here k_slice_pass, or the lm_head epilogue) reduces every 256-column slice of a row
+// to either a Gumbel winner (rows without top-k/top-p) or its maximum raw logit (rows with).
+// Pass 2 (k_select, one 8-CTA cluster per row) turns the slice maxima into a lower bound tau
+// on the k-th largest logit (the k-th largest slice maximum: k disjoint slices each hold a
+// value >= it), re-reads the row, keeps the few columns >= tau, and resolves them exactly:
+// top-k with ties kept (>=, as _sampler_kernels.py:88-90), vLLM's top-p, Philox noise only
+// for the survivors.  Rows that do not fit (top-p without top-k, more ties than the candidate
+// buffer) go through k_fullrow, an exact radix-select pass over the whole row.
+#include <cooperative_groups.h>
+
+#include "lm_head.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace vqk {
+
+constexpr int kClusterSize = 8;
+constexpr int kMaxSlices = 2048;
+constexpr int kLocalCap = 512;    // candidates one CTA of the cluster may collect
+constexpr int kGlobalCap = 1024;  // candidates resolved per row
+constexpr double kMassScale = 1099511627776.0;  // 2^40 fixed point for probability mass
+
+// ---- small block-level helpers ------------------------------------------------------------
+struct Best {
+  float s;
+  int t;
+};
+
+__device__ __forceinline__ Best warp_best(Best b) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float s2 = __shfl_xor_sync(0xffffffffu, b.s, o);
+    int t2 = __shfl_xor_sync(0xffffffffu, b.t, o);
+    if (better(s2, t2, b.s, b.t)) { b.s = s2; b.t = t2; }
+  }
+  return b;
+}
+
+// all threads of the block must call; result valid in every thread
+__device__ Best block_best(Best b, Best* red /* >= 32 */) {
+  b = warp_best(b);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = b;
+  __syncthreads();
+  Best r = (l < nw) ? red[l] : Best{-INFINITY, 0x7fffffff};
+  r = warp_best(r);
+  return r;
+}
+
+__device__ float block_maxf(float v, float* red /* >= 32 */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  v = (l < nw) ? red[l] : -INFINITY;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float ldl(const T* row, int col) { return to_f32<T>(row[col]); }
+
+__device__ __forceinline__ unsigned long long mass_of(float y, float m) {
+  return (unsigned long long)((double)expf(y - m) * kMassScale);
+}
+
+// ---- pass 1 over materialised logits --------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) k_slice_pass(const T* __restrict__ logits, long long ld, int V, SampleDev sp,
+                                                   float* __restrict__ slice_max, float* __restrict__ part_score,
+                                                   int* __restrict__ part_token, int nslices) {
+  const int b = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const int slice = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (slice >= nslices) return;
+  const RowMeta m = decode_row(sp, b);
+  const T* row = logits + (long long)b * ld;
+  const int c0 = slice * 256;
+  float mx = -INFINITY;
+  Best best{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int col = c0 + j * 32 + lane;
+    if (col < V) {
+      const float l = ldl(row, col);
+      if (m.flags & ROW_CAND) {
+        mx = fmaxf(mx, l);
+      } else {
+        float sc = l;
+        if (!(m.flags & ROW_GREEDY)) {
+          sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(col + sp.vocab_offset));
+          if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
+        }
+        if (better(sc, col, best.s, best.t)) { best.s = sc; best.t = col; }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  best = warp_best(best);
+  if (lane == 0) {
+    slice_max[(long long)b * nslices + slice] = mx;
+    part_score[(long long)b * nslices + slice] = best.s;
+    part_token[(long long)b * nslices + slice] = best.t;
+  }
+}
+
+// ---- exact resolution of a small candidate set (one block) ------------------------------------
+// cv/ct: candidate raw logits and GLOBAL token ids in shared memory; work arrays sized n.
+// Returns the winner in every thread.  Must be called by all threads of the block.
+__device__ Best resolve_candidates(const float* cv, const int* ct, int n, const RowMeta& m, float* y,
+                                   unsigned long long* w, unsigned char* alive, Best* red_b, float* red_f,
+                                   unsigned long long* zsum) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  // top-k with ties: alive iff fewer than k candidates are strictly larger
+  for (int i = tid; i < n; i += nt) {
+    bool a = true;
+    if (m.top_k > 0) {
+      const float vi = cv[i];
+      int gcount = 0;
+      for (int j = 0; j < n; ++j) gcount += (cv[j] > vi);
+      a = gcount < m.top_k;
+    } else if (m.flags & ROW_MASK_THR) {
+      a = cv[i] >= m.thr;
+    }
+    alive[i] = a;
+    y[i] = cv[i] / m.T;
+  }
+  __syncthreads();
+  if (m.top_p < 1.f) {
+    float mx = -INFINITY;
+    for (int i = tid; i < n; i += nt)
+      if (alive[i]) mx = fmaxf(mx, y[i]);
+    mx = block_maxf(mx, red_f);
+    if (tid == 0) *zsum = 0ull;
+    __syncthreads();
+    unsigned long long loc = 0;
+    for (int i = tid; i < n; i += nt) {
+      unsigned long long wi = alive[i] ? mass_of(y[i], mx) : 0ull;
+      w[i] = wi;
+      loc += wi;
+    }
+    atomicAdd(zsum, loc);
+    __syncthreads();
+    const double target = (double)m.top_p * (double)(*zsum);
+    __syncthreads();
+    // keep iff the mass strictly above is < p * Z (vLLM: drop while ascending cumsum <= 1 - p)
+    for (int i = tid; i < n; i += nt) {
+      if (!alive[i]) continue;
+      const float yi = y[i];
+      unsigned long long above = 0;
+      for (int j = 0; j < n; ++j)
+        if (alive[j] && y[j] > yi) above += w[j];
+      if (!((double)above < target)) alive[i] = 2;  // dropped; stays non-zero while others still read it
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += nt)
+      if (alive[i] == 2) alive[i] = 0;
+    __syncthreads();
+  }
+  Best best{-INFINITY, 0x7fffffff};
+  for (int i = tid; i < n; i += nt) {
+    if (!alive[i]) continue;
+    const float sc = y[i] + gumbel_noise(m.seed, (uint32_t)ct[i]);
+    if (better(sc, ct[i], best.s, best.t)) { best.s = sc; best.t = ct[i]; }
+  }
+  return block_best(best, red_b);
+}
+
+__device__ __forceinline__ void write_header(uint8_t* records, int b, float score, int token, int n, int flags) {
+  if (!records) return;
+  RecordHeader* h = reinterpret_cast<RecordHeader*>(records + (size_t)b * VQK_RECORD_BYTES);
+  h->score = score; h->token = token; h->n = n; h->flags = flags;
+}
+
+// ---- pass 2: one cluster per row -----------------------------------------------------------------
+template <typename T>
+__global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(256) k_select(const SelectParams p) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (int)cluster.block_rank();
+  const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const RowMeta m = decode_row(p.sp, b);
+
+  __shared__ float s_sm[kMaxSlices];
+  __shared__ Cand s_cand[kLocalCap];
+  __shared__ float s_cv[kGlobalCap];
+  __shared__ int s_ct[kGlobalCap];
+  __shared__ float s_y[kGlobalCap];
+  __shared__ unsigned long long s_w[kGlobalCap];
+  __shared__ unsigned char s_alive[kGlobalCap];
+  __shared__ Best s_redb[32];
+  __shared__ float s_redf[32];
+  __shared__ unsigned long long s_z;
+  __shared__ float s_tau;
+  __shared__ int s_count;
+
+  if (!(m.flags & ROW_CAND)) {
+    // row already reduced to per-slice winners: merge them (rank 0 only, no cluster traffic)
+    if (crank != 0) return;
+    Best best{-INFINITY, 0x7fffffff};
+    for (int s = tid; s < p.nslices; s += blockDim.x) {
+      const float sc = p.part_score[(long long)b * p.nslices + s];
+      const int tk = p.part_token[(long long)b * p.nslices + s];
+      if (better(sc, tk, best.s, best.t)) { best.s = sc; best.t = tk; }
+    }
+    best = block_best(best, s_redb);
+    if (tid == 0) {
+      const long long tok = (long long)best.t + p.sp.vocab_offset;
+      write_header(p.records, b, best.s, (int)tok, 0, 0);
+      if (p.tokens) p.tokens[b] = tok;
+      if (p.scores) p.scores[b] = best.s;
+      p.rowflag[b] = 0;
+    }
+    return;
+  }
+
+  const bool needs_row = (m.flags & ROW_FULLROW) || (m.top_k > 0 && (m.top_k > p.nslices || p.nslices > kMaxSlices));
+  if (needs_row) {  // uniform over the cluster
+    if (crank == 0 && tid == 0) {
+      write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_NEEDS_ROW);
+      p.rowflag[b] = 1;
+      if (!p.single_shard && p.tokens) p.tokens[b] = -1;
+    }
+    return;
+  }
+
+  // ---- tau: k-th largest slice maximum, rank counting split over the cluster --------------
+  if (tid == 0) { s_count = 0; s_tau = m.thr; }
+  if (m.top_k > 0) {
+    const int ns = p.nslices;
+    for (int s = tid; s < ns; s += blockDim.x) s_sm[s] = p.slice_max[(long long)b * ns + s];
+    __syncthreads();
+    cluster.sync();  // every CTA's s_tau / s_count initialised before any remote write
+    const int per = (ns + kClusterSize - 1) / kClusterSize;
+    const int i0 = crank * per, i1 = min(ns, i0 + per);
+    for (int i = i0 + warp; i < i1; i += 8) {
+      const float vi = s_sm[i];
+      int cnt = 0;
+      for (int j = lane; j < ns; j += 32) {
+        const float vj = s_sm[j];
+        cnt += (vj > vi) || (vj == vi && j < i);
+      }
+      cnt = __reduce_add_sync(0xffffffffu, cnt);
+      if (cnt == m.top_k - 1 && lane == 0) {
+#pragma unroll
+        for (int r = 0; r < kClusterSize; ++r) *cluster.map_shared_rank(&s_tau, r) = vi;
+      }
+    }
+  }
+  cluster.sync();
+  const float tau = s_tau;
+
+  // ---- collect the columns >= tau from this CTA's part of the row ---------------------------
+  {
+    const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
+    const int per = ((p.V + kClusterSize - 1) / kClusterSize + 7) & ~7;
+    const int c0 = crank * per, c1 = min(p.V, c0 + per);
+    for (int col = c0 + tid; col < c1; col += blockDim.x) {
+      const float l = ldl(row, col);
+      if (l >= tau) {
+        const int pos = atomicAdd(&s_count, 1);
+        if (pos < kLocalCap) s_cand[pos] = Cand{l, col};
+      }
+    }
+  }
+  cluster.sync();
+
+  // ---- rank 0 gathers all candidates ---------------------------------------------------------
+  __shared__ int s_total, s_over;
+  if (crank == 0) {
+    if (tid == 0) {
+      int tot = 0, over = 0;
+      for (int r = 0; r < kClusterSize; ++r) {
+        const int c = *cluster.map_shared_rank(&s_count, r);
+        if (c > kLocalCap) over = 1;
+        tot += min(c, kLocalCap);
+      }
+      if (tot > kGlobalCap) over = 1;
+      s_total = tot; s_over = over;
+    }
+    __syncthreads();
+    if (!s_over) {
+      int base = 0;
+      for (int r = 0; r < kClusterSize; ++r) {
+        const int c = *cluster.map_shared_rank(&s_count, r);
+        const Cand* rc = cluster.map_shared_rank(&s_cand[0], r);
+        for (int i = tid; i < c; i += blockDim.x) {
+          Cand cd = rc[i];
+          s_cv[base + i] = cd.v;
+          s_ct[base + i] = (int)(cd.t + p.sp.vocab_offset);
+        }
+        base += c;
+      }
+    }
+    __syncthreads();
+  }
+  cluster.sync();  // remote shared memory no longer needed after this point
+  if (crank != 0) return;
+
+  if (s_over) {
+    if (tid == 0) {
+      write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_OVERFLOW);
+      p.rowflag[b] = 1;
+      if (!p.single_shard && p.tokens) p.tokens[b] = -1;
+    }
+    return;
+  }
+  const int n = s_total;
+  if (tid == 0) p.rowflag[b] = 0;
+
+  if (p.records) {
+    // shard record: the local top-k survivors (ties kept); top-p needs the union, so it waits
+    __shared__ int s_nrec;
+    if (tid == 0) s_nrec = 0;
+    __syncthreads();
+    Cand* out = reinterpret_cast<Cand*>(p.records + (size_t)b * VQK_RECORD_BYTES + sizeof(RecordHeader));
+    for (int i = tid; i < n; i += blockDim.x) {
+      bool keep = true;
+      if (m.top_k > 0) {
+        int gc = 0;
+        const float vi = s_cv[i];
+        for (int j = 0; j < n; ++j) gc += (s_cv[j] > vi);
+        keep = gc < m.top_k;
+      }
+      if (keep) {
+        const int pos = atomicAdd(&s_nrec, 1);
+        if (pos < VQK_RECORD_CAP) out[pos] = Cand{s_cv[i], s_ct[i]};
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int nr = s_nrec;
+      write_header(p.records, b, -INFINITY, -1, min(nr, VQK_RECORD_CAP), nr > VQK_RECORD_CAP ? VQK_RECORD_FLAG_OVERFLOW : 0);
+    }
+  }
+  if (p.single_shard) {
+    Best w = resolve_candidates(s_cv, s_ct, n, m, s_y, s_w, s_alive, s_redb, s_redf, &s_z);
+    if (tid == 0) {
+      if (p.tokens) p.tokens[b] = w.t;
+      if (p.scores) p.scores[b] = w.s;
+    }
+  }
+}
+
+// ---- merge of gathered shard records -----------------------------------------------------------
+__global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ records, int G, int B, SampleDev sp,
+                                                  long long* tokens, float* scores) {
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const RowMeta m = decode_row(sp, b);
+  __shared__ float s_cv[kGlobalCap];
+  __shared__ int s_ct[kGlobalCap];
+  __shared__ float s_y[kGlobalCap];
+  __shared__ unsigned long long s_w[kGlobalCap];
+  __shared__ unsigned char s_alive[kGlobalCap];
+  __shared__ Best s_redb[32];
+  __shared__ float s_redf[32];
+  __shared__ unsigned long long s_z;
+  __shared__ int s_n, s_bad;
+  if (tid == 0) {
+    int n = 0, bad = 0;
+    for (int g = 0; g < G; ++g) {
+      const RecordHeader* h = reinterpret_cast<const RecordHeader*>(records + ((size_t)g * B + b) * VQK_RECORD_BYTES);
+      if (h->flags) bad = 1;
+      n += h->n;
+    }
+    if (n > kGlobalCap) bad = 1;
+    s_n = n; s_bad = bad;
+  }
+  __syncthreads();
+  if (s_bad) {
+    if (tid == 0) { tokens[b] = -1; if (scores) scores[b] = -INFINITY; }
+    return;
+  }
+  if (s_n == 0) {  // winners only
+    if (tid == 0) {
+      Best best{-INFINITY, 0x7fffffff};
+      for (int g = 0; g < G; ++g) {
+        const RecordHeader* h = reinterpret_cast<const RecordHeader*>(records + ((size_t)g * B + b) * VQK_RECORD_BYTES);
+        if (better(h->score, h->token, best.s, best.t)) { best.s = h->score; best.t = h->token; }
+      }
+      tokens[b] = best.t;
+      if (scores) scores[b] = best.s;
+    }
+    return;
+  }
+  int base = 0;
+  for (int g = 0; g < G; ++g) {
+    const uint8_t* rec = records + ((size_t)g * B + b) * VQK_RECORD_BYTES;
+    const int c = reinterpret_cast<const RecordHeader*>(rec)->n;
+    const Cand* cd = reinterpret_cast<const Cand*>(rec + sizeof(RecordHeader));
+    for (int i = tid; i < c; i += blockDim.x) { s_cv[base + i] = cd[i].v; s_ct[base + i] = cd[i].t; }
+    base += c;
+  }
+  __syncthreads();
+  Best w = resolve_candidates(s_cv, s_ct, s_n, m, s_y, s_w, s_alive, s_redb, s_redf, &s_z);
+  if (tid == 0) { tokens[b] = w.t; if (scores) scores[b] = w.s; }
+}
+
+// ---- exact full-row pass ---------------------------------------------------------------------------
+// k-th largest raw logit of a row by 8-bit MSB radix select on order-preserving keys.
+template <typename T>
+__device__ float radix_kth_largest(const T* row, int V, int k, unsigned int* hist /* 256 */, unsigned int* bcast /* 2 */) {
+  uint32_t prefix = 0, mask = 0;
+  int kk = k;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int col = threadIdx.x; col < V; col += blockDim.x) {
+      const uint32_t key = f32_key(ldl(row, col));
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int cum = 0;
+      int bin = 255;
+      for (; bin > 0; --bin) {
+        if (cum + hist[bin] >= (unsigned)kk) break;
+        cum += hist[bin];
+      }
+      bcast[0] = (unsigned)bin;
+      bcast[1] = cum;
+    }
+    __syncthreads();
+    prefix |= bcast[0] << shift;
+    mask |= 0xffu << shift;
+    kk -= (int)bcast[1];
+    __syncthreads();
+  }
+  return key_f32(prefix);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024) k_fullrow(const SelectParams p) {
+  const int b = blockIdx.x, tid = threadIdx.x;
+  if (!p.rowflag[b]) return;
+  const RowMeta m = decode_row(p.sp, b);
+  const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
+  const int V = p.V;
+  __shared__ unsigned int s_hist[256];
+  __shared__ unsigned long long s_mass[256];
+  __shared__ unsigned int s_bc[2];
+  __shared__ unsigned long long s_z, s_above;
+  __shared__ Best s_redb[32];
+  __shared__ float s_redf[32];
+
+  float thr = -INFINITY;
+  if (m.top_k > 0) thr = radix_kth_largest(row, V, m.top_k, s_hist, s_bc);
+  else if (m.flags & ROW_MASK_THR) thr = m.thr;
+
+  uint32_t cut = 0;  // smallest surviving key of y; 0 keeps everything
+  if (m.top_p < 1.f) {
+    float mx = -INFINITY;
+    for (int col = tid; col < V; col += blockDim.x) {
+      const float l = ldl(row, col);
+      if (l >= thr) mx = fmaxf(mx, l / m.T);
+    }
+    mx = block_maxf(mx, s_redf);
+    if (tid == 0) { s_z = 0ull; s_above = 0ull; }
+    __syncthreads();
+    unsigned long long loc = 0;
+    for (int col = tid; col < V; col += blockDim.x) {
+      const float l = ldl(row, col);
+      if (l >= thr) loc += mass_of(l / m.T, mx);
+    }
+    atomicAdd(&s_z, loc);
+    __syncthreads();
+    const double target = (double)m.top_p * (double)s_z;
+    uint32_t prefix = 0, mask = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int i = tid; i < 256; i += blockDim.x) s_mass[i] = 0ull;
+      __syncthreads();
+      for (int col = tid; col < V; col += blockDim.x) {
+        const float l = ldl(row, col);
+        if (l >= thr) {
+          const float y = l / m.T;
+          const uint32_t key = f32_key(y);
+          if ((key & mask) == prefix) atomicAdd(&s_mass[(key >> shift) & 0xff], mass_of(y, mx));
+        }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned long long cum = s_above;
+        int bin = 255;
+        for (; bin > 0; --bin) {
+          if ((double)(cum + s_mass[bin]) >= target) break;
+          cum += s_mass[bin];
+        }
+        s_bc[0] = (unsigned)bin;
+        s_above = cum;
+      }
+      __syncthreads();
+      prefix |= s_bc[0] << shift;
+      mask |= 0xffu << shift;
+      __syncthreads();
+    }
+    cut = prefix;
+  }
+
+  Best best{-INFINITY, 0x7fffffff};
+  for (int col = tid; col < V; col += blockDim.x) {
+    const float l = ldl(row, col);
+    if (!(l >= thr)) continue;
+    const float y = l / m.T;
+    if (f32_key(y) < cut) continue;
+    const int tok = (int)(col + p.sp.vocab_offset);
+    const float sc = y + gumbel_noise(m.seed, (uint32_t)tok);
+    if (better(sc, tok, best.s, best.t)) { best.s = sc; best.t = tok; }
+  }
+  best = block_best(best, s_redb);
+  if (tid == 0) {
+    if (p.tokens) p.tokens[b] = best.t;
+    if (p.scores) p.scores[b] = best.s;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024) k_topk_threshold(const T* __restrict__ logits, long long ld, int V,
+                                                        const int32_t* __restrict__ top_k, float* __restrict__ thr) {
+  const int b = blockIdx.x;
+  __shared__ unsigned int s_hist[256];
+  __shared__ unsigned int s_bc[2];
+  const int k = top_k[b];
+  if (k <= 0 || k >= V) {
+    if (threadIdx.x == 0) thr[b] = -INFINITY;
+    return;
+  }
+  float t = radix_kth_largest(logits + (long long)b * ld, V, k, s_hist, s_bc);
+  if (threadIdx.x == 0) thr[b] = t;
+}
+
+// ---- host launchers ------------------------------------------------------------------------------------
+#define VQK_DISPATCH_DTYPE(dt, CALL)                          \
+  switch (dt) {                                               \
+    case VQK_F16: { using T = __half; CALL; break; }          \
+    case VQK_BF16: { using T = __nv_bfloat16; CALL; break; }  \
+    case VQK_F32: { using T = float; CALL; break; }           \
+    default: return VQK_ERR_INVALID;                          \
+  }
+
+int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, float* slice_max,
+                      float* part_score, int* part_token, int nslices, cudaStream_t st) {
+  if (B == 0 || V == 0) return VQK_OK;
+  dim3 grid((unsigned)((nslices + 7) / 8), (unsigned)B);
+  VQK_DISPATCH_DTYPE(dtype, (k_slice_pass<T><<<grid, 256, 0, st>>>((const T*)logits, ld, V, sp, slice_max, part_score,
+                                                                   part_token, nslices)));
+  VQK_LAUNCH_CHECK();
+  return VQK_OK;
+}
+
+int launch_select(const SelectParams& p, cudaStream_t st) {
+  if (p.B == 0) return VQK_OK;
+  dim3 grid(kClusterSize, (unsigned)p.B);
+  VQK_DISPATCH_DTYPE(p.dtype, (k_select<T><<<grid, 256, 0, st>>>(p)));
+  VQK_LAUNCH_CHECK();
+  return VQK_OK;
+}
+
+int launch_fullrow(const SelectParams& p, cudaStream_t st) {
+  if (p.B == 0) return VQK_OK;
+  VQK_DISPATCH_DTYPE(p.dtype, (k_fullrow<T><<<(unsigned)p.B, 1024, 0, st>>>(p)));
+  VQK_LAUNCH_CHECK();
+  return VQK_OK;
+}
+
+int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, long long* tokens, float* scores,
+                    cudaStream_t st) {
+  if (B == 0) return VQK_OK;
+  k_finalize<<<(unsigned)B, 256, 0, st>>>(records, G, B, sp, tokens, scores);
+  VQK_LAUNCH_CHECK();
+  return VQK_OK;
+}
+
+int launch_topk_threshold(const void* logits, int dtype, long long ld, int B, int V, const int32_t* top_k, float* thr,
+                          cudaStream_t st) {
+  if (B == 0) return VQK_OK;
+  VQK_DISPATCH_DTYPE(dtype, (k_topk_threshold<T><<<(unsigned)B, 1024, 0, st>>>((const T*)logits, ld, V, top_k, thr)));
+  VQK_LAUNCH_CHECK();
+  return VQK_OK;
+}
+
+}  // namespace vqk

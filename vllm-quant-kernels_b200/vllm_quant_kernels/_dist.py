@@ -1,0 +1,136 @@
+"""Vocab-sharded lm_head + sampler step across the GPUs of one node.
+
+Rows of the lm_head weight are independent, so rank r owns a contiguous vocab
+slice and computes its slice of the logits plus a small per-row *record*: its
+Gumbel winner, or its top-k candidates when top-k / top-p is active.  One tiny
+all-gather of the records (1 KiB per row per rank) is the only exchange; every
+rank then resolves the same final token.  Philox noise is indexed by the GLOBAL
+token id, so the answer does not depend on the number of shards.
+
+The reference plugin is single-GPU; the merge has the shape of vLLM's
+`LogitsProcessor.get_top_tokens` (vllm/model_executor/layers/logits_processor.py:106-156).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _ffi
+from ._lmhead import LMHeadShard, SamplingArgs, finalize_records
+
+ROW_ALIGN = 16  # shard boundaries fall on the kernels' 16-row tiles
+
+
+def shard_bounds(vocab: int, world: int, rank: int) -> Tuple[int, int]:
+    """Rows [start, end) of the global vocabulary owned by `rank`: equal contiguous
+    slices rounded up to a multiple of 16 rows, the last ranks taking what is left."""
+    if not (0 <= rank < world):
+        raise ValueError("rank out of range")
+    per = -(-vocab // world)
+    per = -(-per // ROW_ALIGN) * ROW_ALIGN
+    start = min(vocab, rank * per)
+    return start, min(vocab, start + per)
+
+
+class VqkComm:
+    """NCCL communicator owned by libvqk (bound at run time to the NCCL PyTorch loaded),
+    so the record all-gather is enqueued on the caller's stream with no extra
+    event hand-off.  The unique id travels through torch.distributed's store."""
+
+    def __init__(self, rank: int, world: int, group=None):
+        import torch.distributed as dist
+        L = _ffi.lib()
+        buf = ctypes.create_string_buffer(_ffi.COMM_ID_BYTES)
+        if rank == 0:
+            _ffi.check(L.vqk_comm_unique_id(buf))
+        obj = [buf.raw if rank == 0 else None]
+        dist.broadcast_object_list(obj, src=0, group=group)
+        h = ctypes.c_void_p()
+        _ffi.check(L.vqk_comm_create(obj[0], rank, world, ctypes.byref(h)))
+        self._h = h
+        self.rank, self.world = rank, world
+
+    def allgather(self, send: torch.Tensor) -> torch.Tensor:
+        send = send.contiguous()
+        out = torch.empty((self.world,) + tuple(send.shape), dtype=send.dtype, device=send.device)
+        _ffi.check(_ffi.lib().vqk_comm_allgather(self._h, send.data_ptr(), out.data_ptr(),
+                                                 send.numel() * send.element_size(),
+                                                 torch.cuda.current_stream(send.device).cuda_stream))
+        return out
+
+    def close(self):
+        if self._h:
+            _ffi.lib().vqk_comm_destroy(self._h)
+            self._h = None
+
+
+def exchange_records(rec: torch.Tensor, group=None, comm: Optional[VqkComm] = None) -> torch.Tensor:
+    """All-gather per-rank records [B, 1024] into [G, B, 1024] (rank-major).  With a
+    VqkComm the collective runs on the current CUDA stream; otherwise through
+    torch.distributed (NCCL for CUDA tensors, gloo for CPU tensors)."""
+    if comm is not None:
+        return comm.allgather(rec)
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    out = torch.empty((world,) + tuple(rec.shape), dtype=rec.dtype, device=rec.device)
+    if rec.is_cuda:
+        dist.all_gather_into_tensor(out, rec.contiguous(), group=group)
+    else:
+        parts = [out[i] for i in range(world)]
+        dist.all_gather(parts, rec.contiguous(), group=group)
+    return out
+
+
+class VocabShardedLMHead:
+    """One rank's part of a vocab-sharded lm_head + sampler step."""
+
+    def __init__(self, shard: LMHeadShard, vocab_start: int, vocab_total: int, group=None,
+                 comm: Optional[VqkComm] = None):
+        self.shard = shard
+        self.vocab_start = int(vocab_start)
+        self.vocab_total = int(vocab_total)
+        self.group = group
+        self.comm = comm
+
+    def local_args(self, sp: SamplingArgs) -> SamplingArgs:
+        return SamplingArgs(sp.temperature, sp.seeds, sp.top_k, sp.top_p, sp.topk_threshold,
+                            vocab_offset=self.vocab_start, vocab_total=self.vocab_total)
+
+    def step(self, hidden_states: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None):
+        """(tokens int64 [B], scores fp32 [B]), identical on every rank."""
+        lsp = self.local_args(sp)
+        rec = self.shard.shard_records(hidden_states, lsp, bias)
+        gathered = exchange_records(rec, self.group, self.comm)
+        return finalize_records(gathered, lsp)
+
+
+# ---- record layout helpers (host side; used by tools and tests) -----------------------
+
+_HDR = np.dtype([("score", "<f4"), ("token", "<i4"), ("n", "<i4"), ("flags", "<i4")])
+_CAND = np.dtype([("v", "<f4"), ("t", "<i4")])
+
+
+def pack_record(score: float = float("-inf"), token: int = -1, cands=(), flags: int = 0) -> np.ndarray:
+    """One 1 KiB record as uint8: the 16-byte header then up to 126 (raw logit, token) pairs."""
+    if len(cands) > _ffi.RECORD_CAP:
+        raise ValueError("too many candidates for one record")
+    buf = np.zeros(_ffi.RECORD_BYTES, dtype=np.uint8)
+    hdr = buf[:16].view(_HDR)
+    hdr["score"], hdr["token"], hdr["n"], hdr["flags"] = score, token, len(cands), flags
+    body = buf[16:16 + 8 * len(cands)].view(_CAND)
+    for i, (v, t) in enumerate(cands):
+        body[i] = (v, t)
+    return buf
+
+
+def unpack_record(buf) -> dict:
+    buf = np.ascontiguousarray(np.asarray(buf, dtype=np.uint8))
+    hdr = buf[:16].view(_HDR)[0]
+    n = int(hdr["n"])
+    body = buf[16:16 + 8 * n].view(_CAND)
+    return dict(score=float(hdr["score"]), token=int(hdr["token"]), n=n, flags=int(hdr["flags"]),
+                cands=[(float(c["v"]), int(c["t"])) for c in body])

@@ -1,0 +1,321 @@
+"""Host side of the quantized lm_head + fused sampler, free of any vLLM import.
+
+Thin: shape checks, output allocation through torch, and one C-ABI call per
+operation on the current CUDA stream.  `_quant.py` / `_sampler.py` wrap these in
+the reference plugin's vLLM classes.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _ffi
+
+MODES = {"int8": _ffi.MODE_W8A16, "w8a8": _ffi.MODE_W8A8, "fp8": _ffi.MODE_FP8,
+         "mxfp8": _ffi.MODE_MXFP8, "mxfp4": _ffi.MODE_MXFP4}
+GROUP = 32
+
+_DT = {torch.float16: _ffi.F16, torch.bfloat16: _ffi.BF16, torch.float32: _ffi.F32}
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: these operators have no CPU path")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# --------------------------------------------------------------------------
+# quantizers
+# --------------------------------------------------------------------------
+
+def quantize_weight(mode: str, w: torch.Tensor):
+    """Offline weight quantisation in the reference's storage layouts
+    (reference: _quant.py:245-380).  Returns (codes, scales):
+    int8 -> int8 [V,H] + fp16 [V]; w8a8 -> int8 + fp32; fp8 -> int8 view of e4m3
+    + fp16; mxfp8 -> uint8 [V,H] + uint8 [V,H/32]; mxfp4 -> uint8 [V,H/2] + uint8 [V,H/32]."""
+    _require_cuda(w, "weight")
+    assert w.dim() == 2 and w.dtype in _DT
+    if w.stride(1) != 1:
+        w = w.contiguous()
+    V, H = w.shape
+    m = MODES[mode]
+    dev = w.device
+    if mode in ("mxfp8", "mxfp4"):
+        assert H % GROUP == 0, f"K={H} must be divisible by group_size={GROUP}"
+    if mode == "mxfp4":
+        q = torch.empty(V, H // 2, dtype=torch.uint8, device=dev)
+    elif mode == "mxfp8":
+        q = torch.empty(V, H, dtype=torch.uint8, device=dev)
+    else:
+        q = torch.empty(V, H, dtype=torch.int8, device=dev)
+    if mode in ("int8", "fp8"):
+        s = torch.empty(V, dtype=torch.float16, device=dev)
+    elif mode == "w8a8":
+        s = torch.empty(V, dtype=torch.float32, device=dev)
+    else:
+        s = torch.empty(V, H // GROUP, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _ffi.check(_ffi.lib().vqk_quantize_weight(m, w.data_ptr(), _DT[w.dtype], V, H, w.stride(0),
+                                                  q.data_ptr(), s.data_ptr(), _stream(w)))
+    return q, s
+
+
+def quantize_act(mode: str, x: torch.Tensor):
+    """Runtime activation quantisation (reference: _quant.py:413,448,495,536-540).
+    Returns (xq, xs); xs is None (int8, fp8), a 1-element fp32 device tensor (w8a8,
+    no host sync) or uint8 [B, H/32] (mx modes)."""
+    _require_cuda(x, "activations")
+    assert x.dim() == 2 and x.dtype in _DT
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    B, H = x.shape
+    dev = x.device
+    xs_ret = None
+    if mode == "int8":
+        xq = torch.empty(B, H, dtype=torch.float16, device=dev)
+        xs = None
+    elif mode == "fp8":
+        xq = torch.empty(B, H, dtype=torch.uint8, device=dev)
+        xs = None
+    elif mode == "w8a8":
+        xq = torch.empty(B, H, dtype=torch.int8, device=dev)
+        xs = torch.empty(2, dtype=torch.float32, device=dev)
+        xs_ret = xs[:1]
+    else:
+        xq = torch.empty(B, H, dtype=torch.uint8, device=dev)
+        xs = torch.empty(B, H // GROUP, dtype=torch.uint8, device=dev)
+        xs_ret = xs
+    with torch.cuda.device(dev):
+        _ffi.check(_ffi.lib().vqk_quantize_act(MODES[mode], x.data_ptr(), _DT[x.dtype], B, H, x.stride(0),
+                                               xq.data_ptr(), _ptr(xs), _stream(x)))
+    return xq, xs_ret
+
+
+# --------------------------------------------------------------------------
+# sampling arguments
+# --------------------------------------------------------------------------
+
+@dataclass
+class SamplingArgs:
+    """Per-row sampling controls, all device tensors of length B (or None).
+    Semantics: include/vqk.h `vqk_sample_params`."""
+    temperature: Optional[torch.Tensor] = None      # fp32; None -> argmax for every row
+    seeds: Optional[torch.Tensor] = None            # int32
+    top_k: Optional[torch.Tensor] = None            # int32; <=0 or >=vocab disables
+    top_p: Optional[torch.Tensor] = None            # fp32; >=1 disables
+    topk_threshold: Optional[torch.Tensor] = None   # fp32 raw-logit threshold (reference style)
+    vocab_offset: int = 0
+    vocab_total: Optional[int] = None
+
+    def to_c(self, B: int, V_local: int) -> _ffi.SampleParams:
+        def chk(t, dt, name):
+            if t is None:
+                return None
+            if t.dtype != dt or t.shape != (B,) or not t.is_cuda or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous CUDA {dt} tensor of shape ({B},)")
+            return t.data_ptr()
+        total = V_local if self.vocab_total is None else int(self.vocab_total)
+        return _ffi.SampleParams(
+            chk(self.temperature, torch.float32, "temperature"), chk(self.seeds, torch.int32, "seeds"),
+            chk(self.top_k, torch.int32, "top_k"), chk(self.top_p, torch.float32, "top_p"),
+            chk(self.topk_threshold, torch.float32, "topk_threshold"), int(self.vocab_offset), total)
+
+
+class _Workspace:
+    """One growing byte buffer per device; torch owns the memory."""
+
+    def __init__(self):
+        self._buf = {}
+
+    def get(self, dev: torch.device, nbytes: int) -> torch.Tensor:
+        key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+        b = self._buf.get(key)
+        if b is None or b.numel() < nbytes:
+            b = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+            self._buf[key] = b
+        return b
+
+
+_WS = _Workspace()
+
+
+# --------------------------------------------------------------------------
+# lm_head shard
+# --------------------------------------------------------------------------
+
+class LMHeadShard:
+    """Quantized rows [V, H] of one vocab shard plus the vqk_lm_head descriptor.
+    Keeps the tensors alive; holds no other device memory."""
+
+    def __init__(self, mode: str, q: torch.Tensor, scales: torch.Tensor, K: Optional[int] = None):
+        _require_cuda(q, "quantized weight")
+        assert q.is_contiguous() and scales.is_contiguous()
+        self.mode = mode
+        self.q = q
+        self.scales = scales
+        self.V = q.shape[0]
+        self.H = int(K) if K is not None else (q.shape[1] * 2 if mode == "mxfp4" else q.shape[1])
+        self.device = q.device
+        h = ctypes.c_void_p()
+        _ffi.check(_ffi.lib().vqk_lm_head_create(MODES[mode], q.data_ptr(), scales.data_ptr(), self.V, self.H,
+                                                 ctypes.byref(h)))
+        self._h = h
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            try:
+                _ffi.lib().vqk_lm_head_destroy(h)
+            except Exception:
+                pass
+            self._h = None
+
+    def set_kernel_events(self, start: Optional["torch.cuda.Event"], stop: Optional["torch.cuda.Event"]) -> None:
+        """Measurement aid: record these CUDA events around the weight-streaming kernel of
+        every following call (None, None switches it off).  The events must have been
+        recorded once so that torch has created their handles."""
+        a = None if start is None else start.cuda_event
+        b = None if stop is None else stop.cuda_event
+        _ffi.check(_ffi.lib().vqk_lm_head_set_kernel_events(self._h, a, b))
+
+    def _x2d(self, x: torch.Tensor) -> torch.Tensor:
+        _require_cuda(x, "hidden_states")
+        x = x.reshape(-1, self.H)
+        if x.dtype not in (torch.float16, torch.bfloat16):
+            x = x.to(torch.float16)
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        return x
+
+    def _ws(self, B: int, sample: bool):
+        with torch.cuda.device(self.device):
+            n = _ffi.lib().vqk_lm_head_workspace_bytes(self._h, B, 1 if sample else 0)
+        if n < 0:
+            _ffi.check(int(n))
+        return _WS.get(self.device, int(n)), int(n)
+
+    def _forward(self, x, bias, logits, sp, tokens, scores, records):
+        B = x.shape[0]
+        ws, n = self._ws(B, sp is not None)
+        spc = sp.to_c(B, self.V) if sp is not None else None
+        with torch.cuda.device(self.device):
+            _ffi.check(_ffi.lib().vqk_lm_head_forward(
+                self._h, x.data_ptr(), _DT[x.dtype], B, x.stride(0), _ptr(bias),
+                _ptr(logits), logits.stride(0) if logits is not None else 0,
+                ctypes.byref(spc) if spc is not None else None,
+                _ptr(tokens), _ptr(scores), _ptr(records), ws.data_ptr(), n, _stream(x)))
+
+    def logits(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp16 logits [B, V] (reference: every `_*_forward` launcher, _quant.py:399-643)."""
+        x2 = self._x2d(x)
+        out = torch.empty(x2.shape[0], self.V, dtype=torch.float16, device=self.device)
+        if bias is not None:
+            bias = bias.to(torch.float16).contiguous()
+        if x2.shape[0]:
+            self._forward(x2, bias, out, None, None, None, None)
+        return out
+
+    def sample(self, x: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None,
+               return_logits: bool = False):
+        """lm_head + sampler in one pass: int64 tokens [B], fp32 winning scores [B]
+        (and the fp16 logits if asked).  Single shard only."""
+        x2 = self._x2d(x)
+        B = x2.shape[0]
+        tokens = torch.empty(B, dtype=torch.int64, device=self.device)
+        scores = torch.empty(B, dtype=torch.float32, device=self.device)
+        out = torch.empty(B, self.V, dtype=torch.float16, device=self.device) if return_logits else None
+        if bias is not None:
+            bias = bias.to(torch.float16).contiguous()
+        if B:
+            self._forward(x2, bias, out, sp, tokens, scores, None)
+        return (tokens, scores, out) if return_logits else (tokens, scores)
+
+    def shard_records(self, x: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """lm_head + local sampling stage of a vocab-sharded step: uint8 [B, 1024]
+        exchange records to be all-gathered and passed to `finalize_records`."""
+        x2 = self._x2d(x)
+        B = x2.shape[0]
+        rec = torch.empty(B, _ffi.RECORD_BYTES, dtype=torch.uint8, device=self.device)
+        if bias is not None:
+            bias = bias.to(torch.float16).contiguous()
+        if B:
+            self._forward(x2, bias, None, sp, None, None, rec)
+        return rec
+
+
+# --------------------------------------------------------------------------
+# stand-alone sampler entry points
+# --------------------------------------------------------------------------
+
+def sample_logits(logits: torch.Tensor, sp: SamplingArgs, records: bool = False):
+    """Sampler on materialised logits [B, V] (fp32 / bf16 / fp16).  Returns
+    (tokens int64, scores fp32), or the uint8 [B, 1024] shard records if `records`."""
+    _require_cuda(logits, "logits")
+    assert logits.dim() == 2 and logits.dtype in _DT
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    B, V = logits.shape
+    dev = logits.device
+    L = _ffi.lib()
+    n = int(L.vqk_sample_workspace_bytes(B, V))
+    if n < 0:
+        _ffi.check(n)
+    ws = _WS.get(dev, n)
+    spc = sp.to_c(B, V)
+    tokens = scores = rec = None
+    if records:
+        rec = torch.empty(B, _ffi.RECORD_BYTES, dtype=torch.uint8, device=dev)
+    else:
+        tokens = torch.empty(B, dtype=torch.int64, device=dev)
+        scores = torch.empty(B, dtype=torch.float32, device=dev)
+    if B:
+        with torch.cuda.device(dev):
+            _ffi.check(L.vqk_sample(logits.data_ptr(), _DT[logits.dtype], B, V, logits.stride(0), ctypes.byref(spc),
+                                    _ptr(tokens), _ptr(scores), _ptr(rec), ws.data_ptr(), n, _stream(logits)))
+    return rec if records else (tokens, scores)
+
+
+def finalize_records(gathered: torch.Tensor, sp: SamplingArgs):
+    """Merge all-gathered shard records [G, B, 1024] into (tokens, scores); every
+    rank gets the same answer.  Rows that overflowed a record get token -1."""
+    _require_cuda(gathered, "records")
+    assert gathered.dtype == torch.uint8 and gathered.dim() == 3 and gathered.shape[2] == _ffi.RECORD_BYTES
+    gathered = gathered.contiguous()
+    G, B, _ = gathered.shape
+    dev = gathered.device
+    tokens = torch.empty(B, dtype=torch.int64, device=dev)
+    scores = torch.empty(B, dtype=torch.float32, device=dev)
+    total = sp.vocab_total if sp.vocab_total is not None else 0
+    spc = sp.to_c(B, total)
+    if B:
+        with torch.cuda.device(dev):
+            _ffi.check(_ffi.lib().vqk_sample_finalize(gathered.data_ptr(), G, B, ctypes.byref(spc), tokens.data_ptr(),
+                                                      scores.data_ptr(), _stream(gathered)))
+    return tokens, scores
+
+
+def topk_threshold(logits: torch.Tensor, top_k: torch.Tensor) -> torch.Tensor:
+    """Per-row k-th largest raw logit on the device, no host sync
+    (reference: _sampler.py:62-93).  Rows with k <= 0 or k >= V get -inf."""
+    _require_cuda(logits, "logits")
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    B, V = logits.shape
+    k = top_k.to(torch.int32).contiguous()
+    thr = torch.empty(B, dtype=torch.float32, device=logits.device)
+    if B:
+        with torch.cuda.device(logits.device):
+            _ffi.check(_ffi.lib().vqk_topk_threshold(logits.data_ptr(), _DT[logits.dtype], B, V, logits.stride(0),
+                                                     k.data_ptr(), thr.data_ptr(), _stream(logits)))
+    return thr
