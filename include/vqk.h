@@ -55,6 +55,10 @@ int vqk_version(void);
 const char* vqk_strerror(int status);
 /* cudaError_t of the most recent failing CUDA call on this host thread (0 if none). */
 int vqk_last_cuda_error(void);
+/* Synchronises the device and returns 1 if a bounded wait inside a kernel ever ran out
+ * (the kernel then drained and left its outputs undefined), 0 if not, -1 on a CUDA error.
+ * For tests and post-mortems; not for the hot path. */
+int vqk_device_error(void);
 
 /* ---------------------------------------------------------------------------
  * Offline weight quantisation.  Replaces the torch code in

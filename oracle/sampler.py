@@ -215,3 +215,25 @@ def synth_logits(B: int, V: int, seed: int = 0, dtype=np.float32):
         cols = rng.choice(V, size=min(5, V), replace=False)
         L[i, cols] = 12.0
     return L.astype(dtype)
+
+
+def resolve_candidates(values, tokens, T, seed, top_k=0, top_p=1.0):
+    """Final choice among a candidate set that is known to contain every logit >= the
+    k-th largest (the union of the shards' records).  Same semantics as :func:`sample`
+    restricted to those candidates; noise by GLOBAL token id.  Returns (token, score)."""
+    v = np.asarray(values, dtype=F32)
+    t = np.asarray(tokens, dtype=np.int64)
+    keep = np.ones(len(v), bool)
+    if top_k and top_k > 0:
+        kth = np.sort(v)[::-1][min(top_k, len(v)) - 1]
+        keep &= v >= kth
+    y = (v / F32(T)).astype(F32)
+    if top_p < 1.0:
+        idx = np.nonzero(keep)[0]
+        k2, _ = top_p_keep(y[idx], top_p)
+        keep2 = np.zeros(len(v), bool)
+        keep2[idx[k2]] = True
+        keep = keep2
+    s = np.where(keep, (y + gumbel(int(seed), t)).astype(F32), F32(-np.inf))
+    order = np.lexsort((t, -s.astype(np.float64)))     # highest score, then lowest token
+    return int(t[order[0]]), F32(s[order[0]])

@@ -64,11 +64,12 @@ def sample_args(B, device, temperature=None, seeds=None, top_k=None, top_p=None,
                         dev(top_p, torch.float32), dev(thr, torch.float32), vocab_offset, vocab_total)
 
 
-def assert_tokens_match(tok_gpu, ref, min_margin=1e-4, min_p_margin=1e-5, what=""):
+def assert_tokens_match(tok_gpu, ref, min_margin=1e-4, min_p_margin=2e-6, what=""):
     """Token ids equal wherever the oracle's top-2 perturbed-score margin and top-p
     boundary margin are not razor thin."""
     tok = t2n(tok_gpu)
     strict = (ref["margin"] > min_margin) & (ref["p_margin"] > min_p_margin)
     bad = (tok != ref["tokens"]) & strict
     assert not bad.any(), f"{what}: rows {np.nonzero(bad)[0][:8]} got {tok[bad][:8]} want {ref['tokens'][bad][:8]}"
-    assert strict.mean() > 0.9, f"{what}: too few rows with a usable margin"
+    # the gate must actually bite: most rows have to be decided, not excused
+    assert strict.mean() >= 0.5, f"{what}: too few rows with a usable margin ({strict.mean():.2f})"

@@ -119,6 +119,8 @@ extern "C" const char* vqk_strerror(int s) {
 
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
+extern "C" int vqk_device_error(void) { return stream_error_flag(); }
+
 extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
                                   vqk_lm_head** out) {
   if (!out) return VQK_ERR_INVALID;
@@ -177,7 +179,12 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   const int sms = device_sm_count();
   const int nslices = sms * 4;
   const int mode = h->mode;
-  const int maxcols = stream_max_cols(mode, (int)h->H);
+  // bulk-copy pipeline when the shape allows it, register-streaming kernel otherwise
+  const char* kenv = getenv("VQK_LM_HEAD_KERNEL");  // "stream" pins the register-streaming kernel (A/B runs)
+  const bool force_v1 = kenv && !strcmp(kenv, "stream");
+  int maxcols = tma_max_cols(mode, (int)h->H);
+  const bool use_tma = !force_v1 && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
+  if (!use_tma) maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
 
   LmHeadWs ws = carve_lm_head(workspace, mode, h->V, h->H, B, sp != nullptr, nslices);
@@ -222,7 +229,7 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
       p.cand_logits = ws.cand + (size_t)b0 * ws.ld_cand;
       p.ld_cand = ws.ld_cand;
     }
-    rc = launch_lm_head_stream(mode, p, sms, st);
+    rc = use_tma ? launch_lm_head_tma(mode, p, sms, st) : launch_lm_head_stream(mode, p, sms, st);
     if (rc) return rc;
   }
   if (h->ev_stop) VQK_CUDA(cudaEventRecord(h->ev_stop, st));

@@ -24,12 +24,18 @@ struct LmHeadParams {
   int nslices;
   __half* cand_logits; // [B, ld_cand] fp16 logits of candidate-path rows (scratch or == logits)
   long long ld_cand;
+  int contig;          // 1: each warp of a group takes a contiguous K range; 0: k-steps interleaved
 };
 
 // lm_head_stream.cu
 size_t stream_smem_bytes(int mode, int K, int NT);
 int stream_max_cols(int mode, int K);  // batch columns one launch can take (0: K too large)
 int launch_lm_head_stream(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
+
+// lm_head_tma.cu: bulk-copy pipeline; needs V % 16 == 0, 16-byte aligned rows and scales
+int tma_max_cols(int mode, int K);     // batch columns per launch (0: shape not covered)
+int launch_lm_head_tma(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
+int stream_error_flag();               // 1 if a bounded wait inside the kernel ever expired (synchronises)
 
 // quantize.cu
 int quantize_act_dispatch(int mode, const void* x, int dt, long long B, long long H, long long ldx, void* xq,

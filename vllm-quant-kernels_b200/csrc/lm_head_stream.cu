@@ -9,6 +9,8 @@
 //
 // Replaces int8_gmv / int8_gemm / fp8_gemm / int8_w8a8_gemm / mxfp8_gemm / mxfp4_gemm of the
 // reference (src/vllm_quant_kernels/_kernels.py) for batch <= 32.
+#include <stdlib.h>
+
 #include "lm_head.cuh"
 
 namespace vqk {
@@ -192,13 +194,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
 
     if constexpr (!MX) {
       constexpr int U = 6;
-      for (int ks0 = wq; ks0 < nks; ks0 += 4 * U) {
+      const int per = (nks + 3) / 4;  // k-steps per warp
+      for (int j0 = 0; j0 < per; j0 += U) {
         uint4 a[U], b[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          int ks = ks0 + 4 * u;
-          int off = ks * 64 + t * 16;
-          if (off + 16 <= K) {
+          const int j = j0 + u;
+          const int ks = p.contig ? wq * per + j : wq + 4 * j;
+          const int off = ks * 64 + t * 16;
+          if (j < per && off + 16 <= K) {
             a[u] = ldg_stream16(pA + off);
             b[u] = ldg_stream16(pB + off);
           } else {
@@ -208,8 +212,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          int ks = ks0 + 4 * u;
-          if (ks < nks) {
+          const int j = j0 + u;
+          const int ks = p.contig ? wq * per + j : wq + 4 * j;
+          if (j < per && ks < nks) {
             const uint32_t wa[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
             const uint32_t wb[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
             if constexpr (MODE == VQK_MODE_W8A16) {
@@ -425,7 +430,10 @@ int stream_max_cols(int mode, int K) {
   return 0;
 }
 
-int launch_lm_head_stream(int mode, const LmHeadParams& p, int grid, cudaStream_t st) {
+int launch_lm_head_stream(int mode, const LmHeadParams& p_in, int grid, cudaStream_t st) {
+  static const int contig = [] { const char* e = getenv("VQK_STREAM_CONTIG"); return e ? atoi(e) : 1; }();
+  LmHeadParams p = p_in;
+  p.contig = contig;
   int NT = p.B <= 8 ? 1 : (p.B <= 16 ? 2 : 4);
   if (NT * 8 > stream_max_cols(mode, p.K)) return VQK_ERR_UNSUPPORTED;
   switch (mode) {

@@ -21,7 +21,7 @@ COMM_ID_BYTES = 128
 
 # every symbol include/vqk.h declares
 SYMBOLS = (
-    "vqk_version", "vqk_strerror", "vqk_last_cuda_error", "vqk_quantize_weight", "vqk_quantize_act",
+    "vqk_version", "vqk_strerror", "vqk_last_cuda_error", "vqk_device_error", "vqk_quantize_weight", "vqk_quantize_act",
     "vqk_lm_head_create", "vqk_lm_head_destroy", "vqk_lm_head_workspace_bytes", "vqk_lm_head_forward",
     "vqk_lm_head_set_kernel_events",
     "vqk_sample_workspace_bytes", "vqk_sample", "vqk_sample_finalize", "vqk_topk_threshold",
@@ -59,6 +59,7 @@ def lib() -> ctypes.CDLL:
     L.vqk_strerror.restype = c_char_p
     L.vqk_strerror.argtypes = [c_int]
     L.vqk_last_cuda_error.restype = c_int
+    L.vqk_device_error.restype = c_int
     L.vqk_quantize_weight.argtypes = [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]
     L.vqk_quantize_act.argtypes = [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]
     L.vqk_lm_head_create.argtypes = [c_int, c_void_p, c_void_p, c_int64, c_int64, POINTER(c_void_p)]
@@ -81,7 +82,7 @@ def lib() -> ctypes.CDLL:
     L.vqk_comm_destroy.argtypes = [c_void_p]
     for name in SYMBOLS:
         fn = getattr(L, name)
-        if fn.restype is c_int and name not in ("vqk_version", "vqk_last_cuda_error"):
+        if fn.restype is c_int and name not in ("vqk_version", "vqk_last_cuda_error", "vqk_device_error"):
             fn.restype = c_int
     _lib = L
     return L
