@@ -179,11 +179,12 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   const int sms = device_sm_count();
   const int nslices = sms * 4;
   const int mode = h->mode;
-  // bulk-copy pipeline when the shape allows it, register-streaming kernel otherwise
-  const char* kenv = getenv("VQK_LM_HEAD_KERNEL");  // "stream" pins the register-streaming kernel (A/B runs)
-  const bool force_v1 = kenv && !strcmp(kenv, "stream");
-  int maxcols = tma_max_cols(mode, (int)h->H);
-  const bool use_tma = !force_v1 && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
+  // The register-streaming kernel is the default (measured faster on B200); VQK_LM_HEAD_KERNEL=tma
+  // selects the bulk-copy pipeline where the shape allows it (A/B runs).
+  const char* kenv = getenv("VQK_LM_HEAD_KERNEL");
+  const bool want_tma = kenv && !strcmp(kenv, "tma");
+  int maxcols = want_tma ? tma_max_cols(mode, (int)h->H) : 0;
+  const bool use_tma = want_tma && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
   if (!use_tma) maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
 

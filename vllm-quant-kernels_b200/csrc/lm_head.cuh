@@ -24,7 +24,6 @@ struct LmHeadParams {
   int nslices;
   __half* cand_logits; // [B, ld_cand] fp16 logits of candidate-path rows (scratch or == logits)
   long long ld_cand;
-  int contig;          // 1: each warp of a group takes a contiguous K range; 0: k-steps interleaved
 };
 
 // lm_head_stream.cu

@@ -12,6 +12,7 @@
 #include <stdlib.h>
 
 #include "lm_head.cuh"
+#include "mma_helpers.cuh"
 
 namespace vqk {
 
@@ -25,58 +26,23 @@ __device__ __forceinline__ uint32_t ldg_stream4(const uint8_t* p) {
   return __ldcs(reinterpret_cast<const unsigned int*>(p));
 }
 
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                       uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// four int8 -> two half2 holding the exact integer values: (b ^ 0x80) | 0x6400 is 1024 + (b + 128)
-__device__ __forceinline__ void int8x4_to_half2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  uint32_t x = w ^ 0x80808080u;
-  uint32_t l = __byte_perm(x, 0x64646464u, 0x4140);
-  uint32_t h = __byte_perm(x, 0x64646464u, 0x4342);
-  const uint32_t bias = 0x64806480u;  // half2(1152, 1152)
-  __half2 lh = __hsub2(*reinterpret_cast<__half2*>(&l), *reinterpret_cast<const __half2*>(&bias));
-  __half2 hh = __hsub2(*reinterpret_cast<__half2*>(&h), *reinterpret_cast<const __half2*>(&bias));
-  lo = *reinterpret_cast<uint32_t*>(&lh);
-  hi = *reinterpret_cast<uint32_t*>(&hh);
-}
-
-// eight packed E2M1 nibbles (element j in nibble j) -> two words of four e4m3 bytes
-__device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  const uint32_t LUT_LO = 0x3C383000u;  // 0, 0.5, 1, 1.5
-  const uint32_t LUT_HI = 0x4C484440u;  // 2, 3, 4, 6
-  uint32_t m0 = __byte_perm(LUT_LO, LUT_HI, w & 0x7777u);
-  uint32_t m1 = __byte_perm(LUT_LO, LUT_HI, (w >> 16) & 0x7777u);
-  uint32_t w4 = w << 4;
-  // msb-replicate mode: output byte j = 0xff if the sign bit of nibble j is set
-  uint32_t s0 = __byte_perm(w4, w, 0xD9C8);
-  uint32_t s1 = __byte_perm(w4, w, 0xFBEA);
-  lo = m0 | (s0 & 0x80808080u);
-  hi = m1 | (s1 & 0x80808080u);
-}
-
 template <int MODE>
 struct AccT { using type = float; };
 template <>
 struct AccT<VQK_MODE_W8A8> { using type = int; };
+
+// one batch of weight data in registers: U 64-byte k-steps of two rows (16 B per lane each), or
+// U scale groups of two rows (8 B / 4 B per lane) plus their E8M0 bytes
+template <int MODE, int U, bool MX = (MODE == VQK_MODE_MXFP8 || MODE == VQK_MODE_MXFP4)>
+struct StreamBuf {
+  uint4 a[U], b[U];
+};
+template <int MODE, int U>
+struct StreamBuf<MODE, U, true> {
+  static constexpr int QW = (MODE == VQK_MODE_MXFP8) ? 2 : 1;
+  uint32_t qa[U][QW], qb[U][QW];
+  uint32_t scA[U / 4], scB[U / 4];
+};
 
 constexpr int kThreads = 512;
 constexpr int kGroups = 4;
@@ -95,7 +61,7 @@ size_t stream_smem_bytes(int mode, int K, int NT) {
          (size_t)NT * 8 * sizeof(RowMeta);
 }
 
-template <int MODE, int NT>
+template <int MODE, int NT, int U, bool EVEN>
 __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadParams p) {
   using acc_t = typename AccT<MODE>::type;
   constexpr bool MX = (MODE == VQK_MODE_MXFP8 || MODE == VQK_MODE_MXFP4);
@@ -121,11 +87,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
       __half h[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
+        // fragment order 0, 2, 1, 3: the weight expansion pairs bytes (0,2) and (1,3) of a word
+        const int kk = k + ((j & 1) * 2) + (j >> 1);
         float v = 0.f;
-        if (b < B && k + j < K) {
+        if (b < B && kk < K) {
           v = p.x_dtype == VQK_BF16
-                  ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.x)[(long long)b * p.ldx + k + j])
-                  : __half2float(reinterpret_cast<const __half*>(p.x)[(long long)b * p.ldx + k + j]);
+                  ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.x)[(long long)b * p.ldx + kk])
+                  : __half2float(reinterpret_cast<const __half*>(p.x)[(long long)b * p.ldx + kk]);
         }
         h[j] = __float2half_rn(v);
       }
@@ -149,13 +117,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
       int l = s & 31, nt = (s >> 5) % NT, G = s / (32 * NT);
       int b = nt * 8 + (l >> 2), k = G * 32 + (l & 3) * 8;
       uint2 v = make_uint2(0, 0);
-      if (b < B) v = *reinterpret_cast<const uint2*>(xq + (long long)b * K + k);
+      if (b < B) {
+        v = *reinterpret_cast<const uint2*>(xq + (long long)b * K + k);
+        if constexpr (MODE == VQK_MODE_MXFP4)  // bytes 0..7 -> (0,2,4,6), (1,3,5,7) like the E2M1 expansion
+          v = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
+      }
       xfrag[s] = v;
     }
+    const float rescale = (MODE == VQK_MODE_MXFP4) ? kE2M1Rescale : 1.0f;
     for (int s = tid; s < ngroups * NT * 8; s += kThreads) {
       int c = s & 7, nt = (s >> 3) % NT, G = s / (8 * NT);
       int b = nt * 8 + c;
-      sxf[s] = b < B ? e8m0_to_f32(xs[(long long)b * ngroups + G]) : 0.f;
+      sxf[s] = b < B ? e8m0_to_f32(xs[(long long)b * ngroups + G]) * rescale : 0.f;
     }
   }
   if (p.do_sample && tid < NT * 8) {
@@ -181,140 +154,171 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   acc_t* myred = red + (size_t)warp * NT * 128;
   const acc_t* gred = red + (size_t)(group * 4) * NT * 128;
 
-  for (int tile = blockIdx.x * kGroups + group; tile < ntiles; tile += gridDim.x * kGroups) {
-    const int row0 = tile * 16;
-    const int rA = min(row0 + g, V - 1), rB = min(row0 + g + 8, V - 1);
-    const uint8_t* pA = p.w + (size_t)rA * rowbytes;
-    const uint8_t* pB = p.w + (size_t)rB * rowbytes;
-    acc_t acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[nt][i] = 0;
+  // ---- main loop: a flat sequence of (tile, batch) steps per warp, double-buffered in
+  // registers: the loads of step n+1 are issued before the MMAs of step n, also across tile
+  // boundaries, so the HBM stream of a warp never waits for its own arithmetic.
+  // EVEN (V % 16 == 0, every warp owns `per` whole units, per % U == 0) removes every bounds
+  // test and zero fill from the inner loop; the instruction count per byte is what decides
+  // whether this kernel reaches the HBM rate.
+  constexpr int UB = MX ? (MODE == VQK_MODE_MXFP8 ? 32 : 16) : 64;   // weight bytes per row and unit
+  constexpr int LB = MX ? (MODE == VQK_MODE_MXFP8 ? 8 : 4) : 16;     // bytes per lane, row and unit
+  constexpr int MM = MX ? 1 : (MODE == VQK_MODE_W8A16 ? 4 : 2);      // MMAs (activation fragments) per unit
+  const int units = MX ? ngroups : nks;
+  const int per = (units + 3) / 4;         // units per warp, contiguous in K
+  const int ubeg = wq * per, uend = EVEN ? ubeg + per : min(units, ubeg + per);
+  const int nb = (per + U - 1) / U;        // batches per tile (same for the 4 warps of a group)
+  const bool sc_aligned = MX && (EVEN || (((ngroups & 3) == 0) && ((per & 3) == 0)));
+  StreamBuf<MODE, U> buf0, buf1;
 
+  auto issue = [&](StreamBuf<MODE, U>& f, int tile, int bi) {
+    const int row0 = tile * 16;
+    const int rA = EVEN ? row0 + g : min(row0 + g, V - 1);
+    const int rB = EVEN ? row0 + g + 8 : min(row0 + g + 8, V - 1);
+    const int u0 = ubeg + bi * U;
+    const uint8_t* pA = p.w + (size_t)rA * rowbytes + (size_t)u0 * UB + t * LB;
+    const uint8_t* pB = p.w + (size_t)rB * rowbytes + (size_t)u0 * UB + t * LB;
     if constexpr (!MX) {
-      constexpr int U = 6;
-      const int per = (nks + 3) / 4;  // k-steps per warp
-      for (int j0 = 0; j0 < per; j0 += U) {
-        uint4 a[U], b[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int j = j0 + u;
-          const int ks = p.contig ? wq * per + j : wq + 4 * j;
-          const int off = ks * 64 + t * 16;
-          if (j < per && off + 16 <= K) {
-            a[u] = ldg_stream16(pA + off);
-            b[u] = ldg_stream16(pB + off);
-          } else {
-            a[u] = make_uint4(0, 0, 0, 0);
-            b[u] = make_uint4(0, 0, 0, 0);
-          }
+      for (int u = 0; u < U; ++u) {
+        if (EVEN || (u0 + u < uend && (u0 + u) * 64 + t * 16 + 16 <= K)) {
+          f.a[u] = ldg_stream16(pA + u * UB);
+          f.b[u] = ldg_stream16(pB + u * UB);
+        } else {
+          f.a[u] = make_uint4(0, 0, 0, 0);
+          f.b[u] = make_uint4(0, 0, 0, 0);
         }
+      }
+    } else {
+      constexpr int QW = StreamBuf<MODE, U>::QW;
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int j = j0 + u;
-          const int ks = p.contig ? wq * per + j : wq + 4 * j;
-          if (j < per && ks < nks) {
-            const uint32_t wa[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
-            const uint32_t wb[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
-            if constexpr (MODE == VQK_MODE_W8A16) {
-              const uint2* xf = xfrag + (size_t)(ks * 4) * NT * 32 + lane;
+      for (int u = 0; u < U; ++u) {
+        if (EVEN || u0 + u < uend) {
+          if constexpr (MODE == VQK_MODE_MXFP8) {
+            uint2 va = ldg_stream8(pA + u * UB), vb = ldg_stream8(pB + u * UB);
+            f.qa[u][0] = va.x; f.qa[u][QW - 1] = va.y; f.qb[u][0] = vb.x; f.qb[u][QW - 1] = vb.y;
+          } else {
+            f.qa[u][0] = ldg_stream4(pA + u * UB);
+            f.qb[u][0] = ldg_stream4(pB + u * UB);
+          }
+        } else {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint32_t a0, a1, a2, a3;
-                int8x4_to_half2x2(wa[i], a0, a2);
-                int8x4_to_half2x2(wb[i], a1, a3);
+          for (int q = 0; q < QW; ++q) { f.qa[u][q] = 0; f.qb[u][q] = 0; }
+        }
+      }
+      const uint8_t* ws = reinterpret_cast<const uint8_t*>(p.wscale);
+      const uint8_t* sA = ws + (size_t)rA * ngroups + u0;
+      const uint8_t* sB = ws + (size_t)rB * ngroups + u0;
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                  uint2 bf = xf[(i * NT + nt) * 32];
-                  mma_f16(acc[nt], a0, a1, a2, a3, bf.x, bf.y);
-                }
+      for (int q = 0; q < U / 4; ++q) {
+        if (EVEN || (sc_aligned && u0 + 4 * q + 4 <= uend)) {
+          f.scA[q] = __ldg(reinterpret_cast<const unsigned int*>(sA + 4 * q));
+          f.scB[q] = __ldg(reinterpret_cast<const unsigned int*>(sB + 4 * q));
+        } else {
+          f.scA[q] = 0; f.scB[q] = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (u0 + 4 * q + j < uend) {
+              f.scA[q] |= (uint32_t)__ldg(sA + 4 * q + j) << (8 * j);
+              f.scB[q] |= (uint32_t)__ldg(sB + 4 * q + j) << (8 * j);
+            }
+        }
+      }
+    }
+  };
+
+  acc_t acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0;
+
+  auto consume = [&](const StreamBuf<MODE, U>& f, int bi) {
+    const int u0 = ubeg + bi * U;
+    const uint2* xf = xfrag + (size_t)u0 * (MM * NT * 32) + lane;   // fragment (unit, i, nt) at ((u*MM+i)*NT+nt)*32
+    if constexpr (!MX) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (EVEN || u0 + u < uend) {
+          const uint32_t wa[4] = {f.a[u].x, f.a[u].y, f.a[u].z, f.a[u].w};
+          const uint32_t wb[4] = {f.b[u].x, f.b[u].y, f.b[u].z, f.b[u].w};
+          if constexpr (MODE == VQK_MODE_W8A16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t a0, a1, a2, a3;
+              int8x4_to_half2_even_odd(wa[i], a0, a2);
+              int8x4_to_half2_even_odd(wb[i], a1, a3);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                uint2 bf = xf[((u * MM + i) * NT + nt) * 32];
+                mma_f16(acc[nt], a0, a1, a2, a3, bf.x, bf.y);
               }
-            } else {
-              const uint2* xf = xfrag + (size_t)(ks * 2) * NT * 32 + lane;
+            }
+          } else {
 #pragma unroll
-              for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < 2; ++i) {
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                  uint2 bf = xf[(i * NT + nt) * 32];
-                  if constexpr (MODE == VQK_MODE_W8A8)
-                    mma_s8(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
-                  else
-                    mma_e4m3(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
-                }
+              for (int nt = 0; nt < NT; ++nt) {
+                uint2 bf = xf[((u * MM + i) * NT + nt) * 32];
+                if constexpr (MODE == VQK_MODE_W8A8)
+                  mma_s8(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
+                else
+                  mma_e4m3(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
               }
             }
           }
         }
       }
     } else {
-      // MX: one MMA per 32-element scale group; warps take chunks of 8 groups round-robin
-      const uint8_t* ws = reinterpret_cast<const uint8_t*>(p.wscale);
-      const uint8_t* sA = ws + (size_t)rA * ngroups;
-      const uint8_t* sB = ws + (size_t)rB * ngroups;
-      const bool sc_aligned = (ngroups & 7) == 0;
-      const int nchunks = (ngroups + 7) / 8;
-      for (int c = wq; c < nchunks; c += 4) {
-        const int G0 = c * 8;
-        uint32_t qa[8][2], qb[8][2];
+      constexpr int QW = StreamBuf<MODE, U>::QW;
+      const float* sxp = sxf + (size_t)u0 * (NT * 8) + 2 * t;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int G = G0 + j;
-          if (G < ngroups) {
-            if constexpr (MODE == VQK_MODE_MXFP8) {
-              uint2 va = ldg_stream8(pA + G * 32 + t * 8), vb = ldg_stream8(pB + G * 32 + t * 8);
-              qa[j][0] = va.x; qa[j][1] = va.y; qb[j][0] = vb.x; qb[j][1] = vb.y;
-            } else {
-              qa[j][0] = ldg_stream4(pA + G * 16 + t * 4);
-              qb[j][0] = ldg_stream4(pB + G * 16 + t * 4);
-              qa[j][1] = 0; qb[j][1] = 0;
-            }
+      for (int u = 0; u < U; ++u) {
+        if (EVEN || u0 + u < uend) {
+          uint32_t a0, a1, a2, a3;
+          if constexpr (MODE == VQK_MODE_MXFP8) {
+            a0 = f.qa[u][0]; a2 = f.qa[u][QW - 1]; a1 = f.qb[u][0]; a3 = f.qb[u][QW - 1];
           } else {
-            qa[j][0] = qa[j][1] = qb[j][0] = qb[j][1] = 0;
+            e2m1x8_to_e4m3_even_odd(f.qa[u][0], a0, a2);
+            e2m1x8_to_e4m3_even_odd(f.qb[u][0], a1, a3);
           }
-        }
-        uint32_t scA[2], scB[2];
-        if (sc_aligned) {
-          uint2 va = __ldg(reinterpret_cast<const uint2*>(sA + G0));
-          uint2 vb = __ldg(reinterpret_cast<const uint2*>(sB + G0));
-          scA[0] = va.x; scA[1] = va.y; scB[0] = vb.x; scB[1] = vb.y;
-        } else {
-          scA[0] = scA[1] = scB[0] = scB[1] = 0;
+          const float fa = e8m0_to_f32((f.scA[u >> 2] >> (8 * (u & 3))) & 0xff);
+          const float fb = e8m0_to_f32((f.scB[u >> 2] >> (8 * (u & 3))) & 0xff);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (G0 + j < ngroups) {
-              scA[j >> 2] |= (uint32_t)__ldg(sA + G0 + j) << (8 * (j & 3));
-              scB[j >> 2] |= (uint32_t)__ldg(sB + G0 + j) << (8 * (j & 3));
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int G = G0 + j;
-          if (G < ngroups) {
-            uint32_t a0, a1, a2, a3;
-            if constexpr (MODE == VQK_MODE_MXFP8) {
-              a0 = qa[j][0]; a2 = qa[j][1]; a1 = qb[j][0]; a3 = qb[j][1];
-            } else {
-              e2m1x8_to_e4m3x8(qa[j][0], a0, a2);
-              e2m1x8_to_e4m3x8(qb[j][0], a1, a3);
-            }
-            const float fa = e8m0_to_f32((scA[j >> 2] >> (8 * (j & 3))) & 0xff);
-            const float fb = e8m0_to_f32((scB[j >> 2] >> (8 * (j & 3))) & 0xff);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              uint2 bf = xfrag[(size_t)(G * NT + nt) * 32 + lane];
-              float2 sx = *reinterpret_cast<const float2*>(sxf + (size_t)(G * NT + nt) * 8 + 2 * t);
-              float d[4] = {0.f, 0.f, 0.f, 0.f};
-              mma_e4m3(d, a0, a1, a2, a3, bf.x, bf.y);
-              acc[nt][0] = fmaf(d[0], fa * sx.x, acc[nt][0]);
-              acc[nt][1] = fmaf(d[1], fa * sx.y, acc[nt][1]);
-              acc[nt][2] = fmaf(d[2], fb * sx.x, acc[nt][2]);
-              acc[nt][3] = fmaf(d[3], fb * sx.y, acc[nt][3]);
-            }
+          for (int nt = 0; nt < NT; ++nt) {
+            uint2 bf = xf[(u * NT + nt) * 32];
+            float2 sx = *reinterpret_cast<const float2*>(sxp + (u * NT + nt) * 8);
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_e4m3(d, a0, a1, a2, a3, bf.x, bf.y);
+            acc[nt][0] = fmaf(d[0], fa * sx.x, acc[nt][0]);
+            acc[nt][1] = fmaf(d[1], fa * sx.y, acc[nt][1]);
+            acc[nt][2] = fmaf(d[2], fb * sx.x, acc[nt][2]);
+            acc[nt][3] = fmaf(d[3], fb * sx.y, acc[nt][3]);
           }
         }
       }
     }
+  };
+
+  const int tstride = gridDim.x * kGroups;
+  int tile = blockIdx.x * kGroups + group, bi = 0, step = 0;
+  bool have = tile < ntiles;
+  if (have) issue(buf0, tile, 0);
+  while (have) {
+    int ntile = tile, nbi = bi + 1;
+    if (nbi == nb) { nbi = 0; ntile = tile + tstride; }
+    const bool nhave = ntile < ntiles;
+    if ((step & 1) == 0) {
+      if (nhave) issue(buf1, ntile, nbi);
+      consume(buf0, bi);
+    } else {
+      if (nhave) issue(buf0, ntile, nbi);
+      consume(buf1, bi);
+    }
+    ++step;
+    const int row0 = tile * 16;
+    const bool tile_done = (bi == nb - 1);
+    tile = ntile; bi = nbi; have = nhave;
+    if (!tile_done) continue;
 
     // ---- cross-warp (split-K) reduction through shared memory --------------------------
 #pragma unroll
@@ -324,6 +328,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
       r[(2 * t + 1) * 16 + g] = acc[nt][1];
       r[(2 * t) * 16 + g + 8] = acc[nt][2];
       r[(2 * t + 1) * 16 + g + 8] = acc[nt][3];
+      acc[nt][0] = 0; acc[nt][1] = 0; acc[nt][2] = 0; acc[nt][3] = 0;
     }
     asm volatile("bar.sync %0, 128;" ::"r"(group + 1));
 
@@ -395,7 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
 }
 
 // ---- host launch -------------------------------------------------------------------------
-template <int MODE, int NT>
+template <int MODE, int NT, int U, bool EVEN>
 static int launch_stream(const LmHeadParams& p, int grid, cudaStream_t st) {
   size_t smem = stream_smem_bytes(MODE, p.K, NT);
   static size_t configured[64] = {};  // per device: largest opt-in so far for this instantiation
@@ -403,21 +408,43 @@ static int launch_stream(const LmHeadParams& p, int grid, cudaStream_t st) {
   VQK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
   if (smem > configured[dev]) {
-    VQK_CUDA(cudaFuncSetAttribute(k_lm_head_stream<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    VQK_CUDA(cudaFuncSetAttribute(k_lm_head_stream<MODE, NT, U, EVEN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)smem));
     configured[dev] = smem;
   }
-  k_lm_head_stream<MODE, NT><<<grid, kThreads, smem, st>>>(p);
+  k_lm_head_stream<MODE, NT, U, EVEN><<<grid, kThreads, smem, st>>>(p);
   VQK_LAUNCH_CHECK();
   return VQK_OK;
+}
+
+// units per batch: the fast variant needs U to divide the units each warp owns
+template <int MODE, int NT>
+static int launch_stream_u(const LmHeadParams& p, int grid, cudaStream_t st) {
+  constexpr bool MX = (MODE == VQK_MODE_MXFP8 || MODE == VQK_MODE_MXFP4);
+  const int units = MX ? p.K / GROUP : (p.K + 63) / 64;
+  const int per = (units + 3) / 4;
+  const bool whole = (p.V % 16 == 0) && (units % 4 == 0) && (MX || p.K % 64 == 0);
+  if constexpr (MODE == VQK_MODE_MXFP4) {
+    if (whole && per % 12 == 0 && per % 16 != 0) return launch_stream<MODE, NT, 12, true>(p, grid, st);
+    if (whole && per % 16 == 0) return launch_stream<MODE, NT, 16, true>(p, grid, st);
+    if (whole && per % 8 == 0) return launch_stream<MODE, NT, 8, true>(p, grid, st);
+    return launch_stream<MODE, NT, 8, false>(p, grid, st);
+  } else if constexpr (MODE == VQK_MODE_MXFP8) {
+    if (whole && per % 8 == 0) return launch_stream<MODE, NT, 8, true>(p, grid, st);
+    return launch_stream<MODE, NT, 8, false>(p, grid, st);
+  } else {
+    if (whole && per % 4 == 0) return launch_stream<MODE, NT, 4, true>(p, grid, st);
+    return launch_stream<MODE, NT, 4, false>(p, grid, st);
+  }
 }
 
 template <int MODE>
 static int launch_stream_nt(const LmHeadParams& p, int NT, int grid, cudaStream_t st) {
   switch (NT) {
-    case 1: return launch_stream<MODE, 1>(p, grid, st);
-    case 2: return launch_stream<MODE, 2>(p, grid, st);
+    case 1: return launch_stream_u<MODE, 1>(p, grid, st);
+    case 2: return launch_stream_u<MODE, 2>(p, grid, st);
     case 4:
-      if constexpr (MODE != VQK_MODE_W8A16) return launch_stream<MODE, 4>(p, grid, st);
+      if constexpr (MODE != VQK_MODE_W8A16) return launch_stream_u<MODE, 4>(p, grid, st);
   }
   return VQK_ERR_INVALID;
 }
@@ -430,10 +457,7 @@ int stream_max_cols(int mode, int K) {
   return 0;
 }
 
-int launch_lm_head_stream(int mode, const LmHeadParams& p_in, int grid, cudaStream_t st) {
-  static const int contig = [] { const char* e = getenv("VQK_STREAM_CONTIG"); return e ? atoi(e) : 1; }();
-  LmHeadParams p = p_in;
-  p.contig = contig;
+int launch_lm_head_stream(int mode, const LmHeadParams& p, int grid, cudaStream_t st) {
   int NT = p.B <= 8 ? 1 : (p.B <= 16 ? 2 : 4);
   if (NT * 8 > stream_max_cols(mode, p.K)) return VQK_ERR_UNSUPPORTED;
   switch (mode) {

@@ -16,6 +16,7 @@
 #include <stdlib.h>
 
 #include "lm_head.cuh"
+#include "mma_helpers.cuh"
 
 namespace vqk {
 
@@ -68,48 +69,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
-}
-
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void int8x4_to_half2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  uint32_t x = w ^ 0x80808080u;
-  uint32_t l = __byte_perm(x, 0x64646464u, 0x4140);
-  uint32_t h = __byte_perm(x, 0x64646464u, 0x4342);
-  const uint32_t bias = 0x64806480u;  // half2(1152, 1152): (b ^ 0x80) | 0x6400 is 1024 + (b + 128)
-  __half2 lh = __hsub2(*reinterpret_cast<__half2*>(&l), *reinterpret_cast<const __half2*>(&bias));
-  __half2 hh = __hsub2(*reinterpret_cast<__half2*>(&h), *reinterpret_cast<const __half2*>(&bias));
-  lo = *reinterpret_cast<uint32_t*>(&lh);
-  hi = *reinterpret_cast<uint32_t*>(&hh);
-}
-__device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  const uint32_t LUT_LO = 0x3C383000u, LUT_HI = 0x4C484440u;  // 0 .5 1 1.5 | 2 3 4 6 as e4m3
-  uint32_t m0 = __byte_perm(LUT_LO, LUT_HI, w & 0x7777u);
-  uint32_t m1 = __byte_perm(LUT_LO, LUT_HI, (w >> 16) & 0x7777u);
-  uint32_t w4 = w << 4;
-  uint32_t s0 = __byte_perm(w4, w, 0xD9C8);  // msb-replicate: byte j = 0xff iff nibble j is negative
-  uint32_t s1 = __byte_perm(w4, w, 0xFBEA);
-  lo = m0 | (s0 & 0x80808080u);
-  hi = m1 | (s1 & 0x80808080u);
 }
 
 template <int MODE>
@@ -186,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_tma(const LmHeadParams 
     for (int s = tid; s < ngroups * NT * 8; s += kThreads) {
       int c = s & 7, nt = (s >> 3) % NT, G = s / (8 * NT);
       int b = nt * 8 + c;
-      sxf[s] = b < B ? e8m0_to_f32(xs[(long long)b * ngroups + G]) : 0.f;
+      sxf[s] = b < B ? e8m0_to_f32(xs[(long long)b * ngroups + G]) * (MODE == VQK_MODE_MXFP4 ? kE2M1Rescale : 1.0f) : 0.f;
     }
   }
   if (p.do_sample && tid < NT * 8) {
@@ -217,9 +176,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_tma(const LmHeadParams 
               __half h[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
+                const int kk = k + ((e & 1) * 2) + (e >> 1);  // order 0, 2, 1, 3 (see int8x4_to_half2_even_odd)
                 float f = p.x_dtype == VQK_BF16
-                              ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.x)[(long long)b * p.ldx + k + e])
-                              : __half2float(reinterpret_cast<const __half*>(p.x)[(long long)b * p.ldx + k + e]);
+                              ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.x)[(long long)b * p.ldx + kk])
+                              : __half2float(reinterpret_cast<const __half*>(p.x)[(long long)b * p.ldx + kk]);
                 h[e] = __float2half_rn(f);
               }
               v = *reinterpret_cast<uint2*>(h);
@@ -229,8 +189,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_tma(const LmHeadParams 
             if (b < B && k + 8 <= K) v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.x) + (long long)b * K + k);
           } else {
             const int G = warp * KPW + j;
-            if (b < B && G < ngroups)
+            if (b < B && G < ngroups) {
               v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.x) + (long long)b * K + G * 32 + t * 8);
+              if constexpr (MODE == VQK_MODE_MXFP4)  // (0,2,4,6), (1,3,5,7) like the E2M1 expansion
+                v = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
+            }
           }
           xf[j][i][nt] = v;
         }
@@ -272,8 +235,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_tma(const LmHeadParams 
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint32_t a0, a1, a2, a3;
-              int8x4_to_half2x2(wa[i], a0, a2);
-              int8x4_to_half2x2(wb[i], a1, a3);
+              int8x4_to_half2_even_odd(wa[i], a0, a2);
+              int8x4_to_half2_even_odd(wb[i], a1, a3);
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt) mma_f16(acc[nt], a0, a1, a2, a3, xf[j][i][nt].x, xf[j][i][nt].y);
             }
@@ -301,8 +264,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_tma(const LmHeadParams 
               uint2 vb = *reinterpret_cast<const uint2*>(rowB + G * 32 + t * 8);
               a0 = va.x; a2 = va.y; a1 = vb.x; a3 = vb.y;
             } else {
-              e2m1x8_to_e4m3x8(*reinterpret_cast<const uint32_t*>(rowA + G * 16 + t * 4), a0, a2);
-              e2m1x8_to_e4m3x8(*reinterpret_cast<const uint32_t*>(rowB + G * 16 + t * 4), a1, a3);
+              e2m1x8_to_e4m3_even_odd(*reinterpret_cast<const uint32_t*>(rowA + G * 16 + t * 4), a0, a2);
+              e2m1x8_to_e4m3_even_odd(*reinterpret_cast<const uint32_t*>(rowB + G * 16 + t * 4), a1, a3);
             }
             const float fa = e8m0_to_f32(sc[g * ngroups + G]);
             const float fb = e8m0_to_f32(sc[(g + 8) * ngroups + G]);

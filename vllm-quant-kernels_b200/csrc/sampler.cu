@@ -257,16 +257,41 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(256) k_se
   const float tau = s_tau;
 
   // ---- collect the columns >= tau from this CTA's part of the row ---------------------------
+  // 16-byte loads, four per thread in flight: this pass is pure L2 latency otherwise
   {
     const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
-    const int per = ((p.V + kClusterSize - 1) / kClusterSize + 7) & ~7;
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const int per = ((p.V + kClusterSize - 1) / kClusterSize + VEC - 1) / VEC * VEC;
     const int c0 = crank * per, c1 = min(p.V, c0 + per);
-    for (int col = c0 + tid; col < c1; col += blockDim.x) {
-      const float l = ldl(row, col);
+    auto push = [&](float l, int col) {
       if (l >= tau) {
         const int pos = atomicAdd(&s_count, 1);
         if (pos < kLocalCap) s_cand[pos] = Cand{l, col};
       }
+    };
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const int nvec = (c1 > c0) ? (c1 - c0) / VEC : 0;  // c0 is a multiple of VEC
+      constexpr int UNR = 4;
+      for (int v0 = tid; v0 < nvec; v0 += blockDim.x * UNR) {
+        uint4 raw[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          const int v = v0 + u * blockDim.x;
+          raw[u] = v < nvec ? *reinterpret_cast<const uint4*>(row + c0 + v * VEC) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          const int v = v0 + u * blockDim.x;
+          if (v < nvec) {
+            const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) push(to_f32<T>(e[j]), c0 + v * VEC + j);
+          }
+        }
+      }
+      for (int col = c0 + nvec * VEC + tid; col < c1; col += blockDim.x) push(ldl(row, col), col);
+    } else {
+      for (int col = c0 + tid; col < c1; col += blockDim.x) push(ldl(row, col), col);
     }
   }
   cluster.sync();
