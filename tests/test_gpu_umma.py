@@ -1,0 +1,78 @@
+"""GPU parity of the tcgen05 tensor-core lm_head kernel (FP8 and W8A8, larger batches)
+against the CPU oracle and against the register-streaming kernel."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lm_head as OLM, sampler as OS
+from tests.util import assert_tokens_match, make_act, make_weight, sample_args, t2n
+
+pytestmark = pytest.mark.gpu
+REL_L2 = 1e-3
+DEV = "cuda"
+
+
+def L():
+    from vllm_quant_kernels import _lmhead
+    return _lmhead
+
+
+def _oracle(mode, x, w, bias=None):
+    wq, ws = OLM.quantize_weight(mode, t2n(w))
+    return OLM.logits(mode, t2n(x), wq, ws, bias=None if bias is None else t2n(bias))
+
+
+@pytest.mark.parametrize("mode", ["fp8", "w8a8"])
+@pytest.mark.parametrize("B,H", [(1, 1024), (16, 3072), (17, 1024), (33, 3072), (64, 1024), (100, 2048),
+                                 (256, 1024), (300, 1024)])
+def test_umma_logits_vs_oracle(mode, B, H, monkeypatch):
+    """Vocab not a multiple of the 128-row tile (TMA zero-fills the ragged tile), batches on both
+    sides of every padded N, more than 256 columns (two launches)."""
+    from vllm_quant_kernels import _ffi
+    V = 16 * 333
+    w = make_weight(V, H, seed=H + B)
+    x = make_act(B, H, seed=B)
+    bias = make_act(1, V, seed=7)[0]
+    q, s = L().quantize_weight(mode, w)
+    shard = L().LMHeadShard(mode, q, s)
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "umma")
+    got = t2n(shard.logits(x, bias))
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "stream")
+    got_stream = t2n(shard.logits(x, bias))
+    monkeypatch.delenv("VQK_LM_HEAD_KERNEL", raising=False)
+    assert _ffi.lib().vqk_device_error() == 0
+    ref = _oracle(mode, x, w, bias)
+    assert OLM.rel_l2(got, ref) <= REL_L2, (mode, B, H, OLM.rel_l2(got, ref))
+    if mode == "w8a8":      # int32 accumulation is exact in both kernels
+        assert (got.view(np.int16) == got_stream.view(np.int16)).all()
+    else:
+        assert OLM.rel_l2(got, got_stream) <= REL_L2
+
+
+@pytest.mark.parametrize("mode", ["fp8", "w8a8"])
+@pytest.mark.parametrize("B", [24, 64, 130])
+def test_umma_fused_sampling(mode, B, monkeypatch):
+    """Default dispatch (batch > 16 -> tensor-core kernel): fused tokens equal the sampler run on
+    the logits the kernel materialises, and the oracle sampler where its margin allows."""
+    V, H = 128 * 391 + 48, 1024
+    w = make_weight(V, H, seed=5) * 4.0
+    x = make_act(B, H, seed=B)
+    q, s = L().quantize_weight(mode, w)
+    shard = L().LMHeadShard(mode, q, s)
+    rng = np.random.default_rng(B)
+    T = rng.uniform(0.5, 1.5, B).astype(np.float32)
+    T[3] = 0.0
+    seeds = rng.integers(0, 2**31 - 1, B).astype(np.int32)
+    monkeypatch.delenv("VQK_LM_HEAD_KERNEL", raising=False)
+    for kw in (dict(), dict(top_k=np.full(B, 50, np.int32), top_p=np.full(B, 0.9, np.float32))):
+        sp = sample_args(B, DEV, T, seeds, **kw)
+        tok, sc, logits = shard.sample(x, sp, return_logits=True)
+        tok2, sc2 = L().sample_logits(logits, sp)
+        assert torch.equal(tok, tok2) and torch.equal(sc, sc2), (mode, B, list(kw))
+        ref = OS.sample(t2n(logits).astype(np.float32), T, seeds, **kw)
+        assert_tokens_match(tok, ref, what=f"umma fused {mode} {list(kw)}")
+        tok3, _ = shard.sample(x, sp)
+        assert torch.equal(tok, tok3)
+    ref_logits = _oracle(mode, x, w)
+    assert OLM.rel_l2(t2n(logits), ref_logits) <= REL_L2

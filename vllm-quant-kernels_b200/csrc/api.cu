@@ -66,7 +66,6 @@ struct LmHeadWs {
   float* part_score;
   int* part_token;
   __half* cand;
-  int* rowflag;
   long long ld_cand;
   size_t total;
 };
@@ -83,7 +82,6 @@ static LmHeadWs carve_lm_head(void* base, int mode, long long V, long long K, lo
     w.part_token = c.take<int>((size_t)B * nslices);
     w.ld_cand = (V + 7) & ~7LL;
     w.cand = c.take<__half>((size_t)B * w.ld_cand);
-    w.rowflag = c.take<int>((size_t)B);
   }
   w.total = (c.off + 255) & ~(size_t)255;
   return w;
@@ -92,6 +90,9 @@ static LmHeadWs carve_lm_head(void* base, int mode, long long V, long long K, lo
 }  // namespace vqk
 
 using namespace vqk;
+
+// batches above this go to the tensor-core kernel (FP8 / W8A8)
+static const int kUmmaMinBatch = 16;
 
 struct vqk_lm_head {
   int mode;
@@ -119,7 +120,10 @@ extern "C" const char* vqk_strerror(int s) {
 
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
-extern "C" int vqk_device_error(void) { return stream_error_flag(); }
+extern "C" int vqk_device_error(void) {
+  const int a = stream_error_flag(), b = umma_error_flag();
+  return (a < 0 || b < 0) ? -1 : (a | b);
+}
 
 extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
                                   vqk_lm_head** out) {
@@ -179,13 +183,20 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   const int sms = device_sm_count();
   const int nslices = sms * 4;
   const int mode = h->mode;
-  // The register-streaming kernel is the default (measured faster on B200); VQK_LM_HEAD_KERNEL=tma
-  // selects the bulk-copy pipeline where the shape allows it (A/B runs).
+  // Kernel choice: the register-streaming kernel for decode batches, the tcgen05 tensor-core
+  // kernel once the batch is large enough that re-streaming the weights per 32 columns (or the
+  // warp-MMA rate) would cost more.  VQK_LM_HEAD_KERNEL = stream | umma | tma pins one (A/B runs;
+  // tma is the bulk-copy pipeline variant of the streaming kernel).
   const char* kenv = getenv("VQK_LM_HEAD_KERNEL");
   const bool want_tma = kenv && !strcmp(kenv, "tma");
+  const bool want_umma = kenv && !strcmp(kenv, "umma");
+  const bool want_stream = kenv && !strcmp(kenv, "stream");
   int maxcols = want_tma ? tma_max_cols(mode, (int)h->H) : 0;
   const bool use_tma = want_tma && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
-  if (!use_tma) maxcols = stream_max_cols(mode, (int)h->H);
+  const int umma_cols = umma_max_cols(mode, (int)h->H);
+  const bool use_umma = !use_tma && !want_stream && umma_cols > 0 && (want_umma || B > kUmmaMinBatch);
+  if (use_umma) maxcols = umma_cols;
+  else if (!use_tma) maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
 
   LmHeadWs ws = carve_lm_head(workspace, mode, h->V, h->H, B, sp != nullptr, nslices);
@@ -230,7 +241,9 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
       p.cand_logits = ws.cand + (size_t)b0 * ws.ld_cand;
       p.ld_cand = ws.ld_cand;
     }
-    rc = use_tma ? launch_lm_head_tma(mode, p, sms, st) : launch_lm_head_stream(mode, p, sms, st);
+    rc = use_umma ? launch_lm_head_umma(mode, p, sms, st)
+         : use_tma ? launch_lm_head_tma(mode, p, sms, st)
+                   : launch_lm_head_stream(mode, p, sms, st);
     if (rc) return rc;
   }
   if (h->ev_stop) VQK_CUDA(cudaEventRecord(h->ev_stop, st));
@@ -242,11 +255,7 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   s.slice_max = ws.slice_max; s.part_score = ws.part_score; s.part_token = ws.part_token; s.nslices = nslices;
   s.records = (uint8_t*)records; s.tokens = (long long*)tokens; s.scores = scores;
   s.single_shard = tokens ? 1 : 0;
-  s.rowflag = ws.rowflag;
-  rc = launch_select(s, st);
-  if (rc) return rc;
-  if (s.single_shard) rc = launch_fullrow(s, st);
-  return rc;
+  return launch_select(s, st);
 }
 
 // ---- stand-alone sampler ----------------------------------------------------------------------
@@ -255,7 +264,6 @@ struct SampleWs {
   float* slice_max;
   float* part_score;
   int* part_token;
-  int* rowflag;
   size_t total;
 };
 SampleWs carve_sample(void* base, long long B, int nslices) {
@@ -264,7 +272,6 @@ SampleWs carve_sample(void* base, long long B, int nslices) {
   w.slice_max = c.take<float>((size_t)B * nslices);
   w.part_score = c.take<float>((size_t)B * nslices);
   w.part_token = c.take<int>((size_t)B * nslices);
-  w.rowflag = c.take<int>((size_t)B);
   w.total = (c.off + 255) & ~(size_t)255;
   return w;
 }
@@ -301,11 +308,7 @@ extern "C" int vqk_sample(const void* logits, int dtype, int64_t B, int64_t V, i
   s.slice_max = ws.slice_max; s.part_score = ws.part_score; s.part_token = ws.part_token; s.nslices = nslices;
   s.records = (uint8_t*)records; s.tokens = (long long*)tokens; s.scores = scores;
   s.single_shard = tokens ? 1 : 0;
-  s.rowflag = ws.rowflag;
-  rc = launch_select(s, st);
-  if (rc) return rc;
-  if (s.single_shard) rc = launch_fullrow(s, st);
-  return rc;
+  return launch_select(s, st);
 }
 
 extern "C" int vqk_sample_finalize(const void* records, int G, int64_t B, const vqk_sample_params* sp, int64_t* tokens,

@@ -36,6 +36,11 @@ int tma_max_cols(int mode, int K);     // batch columns per launch (0: shape not
 int launch_lm_head_tma(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
 int stream_error_flag();               // 1 if a bounded wait inside the kernel ever expired (synchronises)
 
+// lm_head_umma.cu: tcgen05 tensor-core kernel for larger batches (FP8, W8A8; K % 128 == 0)
+int umma_max_cols(int mode, int K);    // 256, or 0 when the mode / shape is not covered
+int launch_lm_head_umma(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
+int umma_error_flag();
+
 // quantize.cu
 int quantize_act_dispatch(int mode, const void* x, int dt, long long B, long long H, long long ldx, void* xq,
                           void* xs, cudaStream_t st);
@@ -56,17 +61,15 @@ struct SelectParams {
   long long* tokens;    // final answers when single shard (may be null)
   float* scores;
   int single_shard;     // 1: also resolve candidate rows to a final token here
-  int* rowflag;         // [B] out: 1 if the row still needs the full-row pass
 };
 
 // first pass over materialised logits: per-slice maxima / Gumbel winners (slices of 256 columns)
 int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, float* slice_max,
                       float* part_score, int* part_token, int nslices, cudaStream_t st);
 inline int slice_pass_nslices(long long V) { return (int)((V + 255) / 256); }
-// cluster-per-row selection: tau from slice maxima, candidate collection, final choice / record
+// cluster-per-row selection: tau from slice maxima, candidate collection, final choice / record;
+// rows that do not fit the candidate scheme are resolved by an exact full-row pass inside
 int launch_select(const SelectParams& p, cudaStream_t st);
-// exact full-row pass for rows flagged in rowflag (top-p without top-k, candidate overflow)
-int launch_fullrow(const SelectParams& p, cudaStream_t st);
 // merge gathered records
 int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, long long* tokens, float* scores,
                     cudaStream_t st);

@@ -7,7 +7,7 @@
 // value >= it), re-reads the row, keeps the few columns >= tau, and resolves them exactly:
 // top-k with ties kept (>=, as _sampler_kernels.py:88-90), vLLM's top-p, Philox noise only
 // for the survivors.  Rows that do not fit (top-p without top-k, more ties than the candidate
-// buffer) go through k_fullrow, an exact radix-select pass over the whole row.
+// buffer) go through fullrow_resolve, an exact radix-select pass over the whole row.
 #include <cooperative_groups.h>
 
 #include "lm_head.cuh"
@@ -179,16 +179,146 @@ __device__ __forceinline__ void write_header(uint8_t* records, int b, float scor
   h->score = score; h->token = token; h->n = n; h->flags = flags;
 }
 
-// ---- pass 2: one cluster per row -----------------------------------------------------------------
+// ---- exact full-row pass ---------------------------------------------------------------------------
+// k-th largest raw logit of a row by 8-bit MSB radix select on order-preserving keys.
 template <typename T>
-__global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(256) k_select(const SelectParams p) {
+__device__ float radix_kth_largest(const T* row, int V, int k, unsigned int* hist /* 256 */, unsigned int* bcast /* 2 */) {
+  uint32_t prefix = 0, mask = 0;
+  int kk = k;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int col = threadIdx.x; col < V; col += blockDim.x) {
+      const uint32_t key = f32_key(ldl(row, col));
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int cum = 0;
+      int bin = 255;
+      for (; bin > 0; --bin) {
+        if (cum + hist[bin] >= (unsigned)kk) break;
+        cum += hist[bin];
+      }
+      bcast[0] = (unsigned)bin;
+      bcast[1] = cum;
+    }
+    __syncthreads();
+    prefix |= bcast[0] << shift;
+    mask |= 0xffu << shift;
+    kk -= (int)bcast[1];
+    __syncthreads();
+  }
+  return key_f32(prefix);
+}
+
+// Scratch of the full-row pass (shared memory of the calling block)
+struct FullRowScratch {
+  unsigned int hist[256];
+  unsigned long long mass[256];
+  unsigned int bc[2];
+  unsigned long long z, above;
+  Best redb[32];
+  float redf[32];
+};
+
+// Exact sampler for one row by passes over the whole row: radix select of the k-th largest
+// raw logit, probability-mass radix select of the nucleus cut, then the Gumbel argmax over
+// the survivors.  Called by every thread of a block; the winner is returned in every thread.
+template <typename T>
+__device__ Best fullrow_resolve(const T* row, int V, const RowMeta& m, long long vocab_offset, FullRowScratch& S) {
+  const int tid = threadIdx.x;
+  unsigned int* s_hist = S.hist;
+  unsigned long long* s_mass = S.mass;
+  unsigned int* s_bc = S.bc;
+  unsigned long long& s_z = S.z;
+  unsigned long long& s_above = S.above;
+  Best* s_redb = S.redb;
+  float* s_redf = S.redf;
+
+  float thr = -INFINITY;
+  if (m.top_k > 0) thr = radix_kth_largest(row, V, m.top_k, s_hist, s_bc);
+  else if (m.flags & ROW_MASK_THR) thr = m.thr;
+
+  uint32_t cut = 0;  // smallest surviving key of y; 0 keeps everything
+  if (m.top_p < 1.f) {
+    float mx = -INFINITY;
+    for (int col = tid; col < V; col += blockDim.x) {
+      const float l = ldl(row, col);
+      if (l >= thr) mx = fmaxf(mx, l / m.T);
+    }
+    mx = block_maxf(mx, s_redf);
+    if (tid == 0) { s_z = 0ull; s_above = 0ull; }
+    __syncthreads();
+    unsigned long long loc = 0;
+    for (int col = tid; col < V; col += blockDim.x) {
+      const float l = ldl(row, col);
+      if (l >= thr) loc += mass_of(l / m.T, mx);
+    }
+    atomicAdd(&s_z, loc);
+    __syncthreads();
+    const double target = (double)m.top_p * (double)s_z;
+    uint32_t prefix = 0, mask = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int i = tid; i < 256; i += blockDim.x) s_mass[i] = 0ull;
+      __syncthreads();
+      for (int col = tid; col < V; col += blockDim.x) {
+        const float l = ldl(row, col);
+        if (l >= thr) {
+          const float y = l / m.T;
+          const uint32_t key = f32_key(y);
+          if ((key & mask) == prefix) atomicAdd(&s_mass[(key >> shift) & 0xff], mass_of(y, mx));
+        }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned long long cum = s_above;
+        int bin = 255;
+        for (; bin > 0; --bin) {
+          if ((double)(cum + s_mass[bin]) >= target) break;
+          cum += s_mass[bin];
+        }
+        s_bc[0] = (unsigned)bin;
+        s_above = cum;
+      }
+      __syncthreads();
+      prefix |= s_bc[0] << shift;
+      mask |= 0xffu << shift;
+      __syncthreads();
+    }
+    cut = prefix;
+  }
+
+  Best best{-INFINITY, 0x7fffffff};
+  for (int col = tid; col < V; col += blockDim.x) {
+    const float l = ldl(row, col);
+    if (!(l >= thr)) continue;
+    const float y = l / m.T;
+    if (f32_key(y) < cut) continue;
+    const int tok = (int)(col + vocab_offset);
+    const float sc = y + gumbel_noise(m.seed, (uint32_t)tok);
+    if (better(sc, tok, best.s, best.t)) { best.s = sc; best.t = tok; }
+  }
+  return block_best(best, s_redb);
+}
+
+// ---- pass 2: one cluster per row -----------------------------------------------------------------
+// Two cluster barriers per row.  Every CTA first puts its share of the row in flight (16-byte
+// loads into registers), then the cluster rank-counts the slice maxima for tau while those loads
+// land; candidates >= tau go straight into rank 0's shared memory through DSMEM atomics, and
+// rank 0 resolves them (or runs the exact full-row pass when the row does not fit).
+constexpr int kSelThreads = 1024;
+constexpr int kSelPreload = 4;  // 16-byte vectors per thread fetched before tau is known
+
+template <typename T>
+__global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (int)cluster.block_rank();
   const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const RowMeta m = decode_row(p.sp, b);
+  const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
 
   __shared__ float s_sm[kMaxSlices];
-  __shared__ Cand s_cand[kLocalCap];
   __shared__ float s_cv[kGlobalCap];
   __shared__ int s_ct[kGlobalCap];
   __shared__ float s_y[kGlobalCap];
@@ -197,8 +327,11 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(256) k_se
   __shared__ Best s_redb[32];
   __shared__ float s_redf[32];
   __shared__ unsigned long long s_z;
-  __shared__ float s_tau;
+  __shared__ float s_tau_slot[kClusterSize];  // rank 0's copy is the one everybody reads
+  __shared__ float s_tau_local;
   __shared__ int s_count;
+  __shared__ int s_nrec;
+  __shared__ FullRowScratch s_full;
 
   if (!(m.flags & ROW_CAND)) {
     // row already reduced to per-slice winners: merge them (rank 0 only, no cluster traffic)
@@ -215,31 +348,51 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(256) k_se
       write_header(p.records, b, best.s, (int)tok, 0, 0);
       if (p.tokens) p.tokens[b] = tok;
       if (p.scores) p.scores[b] = best.s;
-      p.rowflag[b] = 0;
     }
     return;
   }
 
+  // rows the candidate scheme cannot bound: top-p without top-k, or k beyond the slice count
   const bool needs_row = (m.flags & ROW_FULLROW) || (m.top_k > 0 && (m.top_k > p.nslices || p.nslices > kMaxSlices));
-  if (needs_row) {  // uniform over the cluster
-    if (crank == 0 && tid == 0) {
+  if (needs_row) {  // uniform over the cluster: no barrier is ever reached
+    if (crank != 0) return;
+    if (p.single_shard) {
+      Best w = fullrow_resolve(row, p.V, m, p.sp.vocab_offset, s_full);
+      if (tid == 0) {
+        write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_NEEDS_ROW);
+        if (p.tokens) p.tokens[b] = w.t;
+        if (p.scores) p.scores[b] = w.s;
+      }
+    } else if (tid == 0) {
       write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_NEEDS_ROW);
-      p.rowflag[b] = 1;
-      if (!p.single_shard && p.tokens) p.tokens[b] = -1;
+      if (p.tokens) p.tokens[b] = -1;
     }
     return;
+  }
+
+  // ---- put this CTA's share of the row in flight -------------------------------------------
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int per = ((p.V + kClusterSize - 1) / kClusterSize + VEC - 1) / VEC * VEC;
+  const int c0 = min(p.V, crank * per), c1 = min(p.V, c0 + per);
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  const int nvec = vec_ok ? (c1 - c0) / VEC : 0;
+  uint4 pre[kSelPreload];
+#pragma unroll
+  for (int u = 0; u < kSelPreload; ++u) {
+    const int v = tid + u * kSelThreads;
+    pre[u] = v < nvec ? *reinterpret_cast<const uint4*>(row + c0 + v * VEC) : make_uint4(0, 0, 0, 0);
   }
 
   // ---- tau: k-th largest slice maximum, rank counting split over the cluster --------------
-  if (tid == 0) { s_count = 0; s_tau = m.thr; }
+  if (tid == 0) { s_count = 0; s_tau_local = -INFINITY; }
+  float tau = m.thr;
   if (m.top_k > 0) {
     const int ns = p.nslices;
     for (int s = tid; s < ns; s += blockDim.x) s_sm[s] = p.slice_max[(long long)b * ns + s];
     __syncthreads();
-    cluster.sync();  // every CTA's s_tau / s_count initialised before any remote write
-    const int per = (ns + kClusterSize - 1) / kClusterSize;
-    const int i0 = crank * per, i1 = min(ns, i0 + per);
-    for (int i = i0 + warp; i < i1; i += 8) {
+    const int share = (ns + kClusterSize - 1) / kClusterSize;
+    const int i0 = crank * share, i1 = min(ns, i0 + share);
+    for (int i = i0 + warp; i < i1; i += kSelThreads / 32) {
       const float vi = s_sm[i];
       int cnt = 0;
       for (int j = lane; j < ns; j += 32) {
@@ -247,101 +400,66 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(256) k_se
         cnt += (vj > vi) || (vj == vi && j < i);
       }
       cnt = __reduce_add_sync(0xffffffffu, cnt);
-      if (cnt == m.top_k - 1 && lane == 0) {
-#pragma unroll
-        for (int r = 0; r < kClusterSize; ++r) *cluster.map_shared_rank(&s_tau, r) = vi;
-      }
-    }
-  }
-  cluster.sync();
-  const float tau = s_tau;
-
-  // ---- collect the columns >= tau from this CTA's part of the row ---------------------------
-  // 16-byte loads, four per thread in flight: this pass is pure L2 latency otherwise
-  {
-    const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
-    constexpr int VEC = 16 / (int)sizeof(T);
-    const int per = ((p.V + kClusterSize - 1) / kClusterSize + VEC - 1) / VEC * VEC;
-    const int c0 = crank * per, c1 = min(p.V, c0 + per);
-    auto push = [&](float l, int col) {
-      if (l >= tau) {
-        const int pos = atomicAdd(&s_count, 1);
-        if (pos < kLocalCap) s_cand[pos] = Cand{l, col};
-      }
-    };
-    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-      const int nvec = (c1 > c0) ? (c1 - c0) / VEC : 0;  // c0 is a multiple of VEC
-      constexpr int UNR = 4;
-      for (int v0 = tid; v0 < nvec; v0 += blockDim.x * UNR) {
-        uint4 raw[UNR];
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-          const int v = v0 + u * blockDim.x;
-          raw[u] = v < nvec ? *reinterpret_cast<const uint4*>(row + c0 + v * VEC) : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-          const int v = v0 + u * blockDim.x;
-          if (v < nvec) {
-            const T* e = reinterpret_cast<const T*>(&raw[u]);
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) push(to_f32<T>(e[j]), c0 + v * VEC + j);
-          }
-        }
-      }
-      for (int col = c0 + nvec * VEC + tid; col < c1; col += blockDim.x) push(ldl(row, col), col);
-    } else {
-      for (int col = c0 + tid; col < c1; col += blockDim.x) push(ldl(row, col), col);
-    }
-  }
-  cluster.sync();
-
-  // ---- rank 0 gathers all candidates ---------------------------------------------------------
-  __shared__ int s_total, s_over;
-  if (crank == 0) {
-    if (tid == 0) {
-      int tot = 0, over = 0;
-      for (int r = 0; r < kClusterSize; ++r) {
-        const int c = *cluster.map_shared_rank(&s_count, r);
-        if (c > kLocalCap) over = 1;
-        tot += min(c, kLocalCap);
-      }
-      if (tot > kGlobalCap) over = 1;
-      s_total = tot; s_over = over;
+      if (cnt == m.top_k - 1 && lane == 0) s_tau_local = vi;  // ranks are unique: at most one writer in the cluster
     }
     __syncthreads();
-    if (!s_over) {
-      int base = 0;
-      for (int r = 0; r < kClusterSize; ++r) {
-        const int c = *cluster.map_shared_rank(&s_count, r);
-        const Cand* rc = cluster.map_shared_rank(&s_cand[0], r);
-        for (int i = tid; i < c; i += blockDim.x) {
-          Cand cd = rc[i];
-          s_cv[base + i] = cd.v;
-          s_ct[base + i] = (int)(cd.t + p.sp.vocab_offset);
-        }
-        base += c;
-      }
-    }
-    __syncthreads();
+    if (tid == 0) *cluster.map_shared_rank(&s_tau_slot[crank], 0) = s_tau_local;
+    cluster.sync();  // slots and rank 0's counter are set
+    const float* slots = cluster.map_shared_rank(&s_tau_slot[0], 0);
+    tau = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < kClusterSize; ++r) tau = fmaxf(tau, slots[r]);
+  } else {
+    cluster.sync();
   }
-  cluster.sync();  // remote shared memory no longer needed after this point
+
+  // ---- candidates >= tau go to rank 0 ---------------------------------------------------------
+  int* r_count = cluster.map_shared_rank(&s_count, 0);
+  float* r_cv = cluster.map_shared_rank(&s_cv[0], 0);
+  int* r_ct = cluster.map_shared_rank(&s_ct[0], 0);
+  auto push = [&](float l, int col) {
+    if (l >= tau) {
+      const int pos = atomicAdd(r_count, 1);
+      if (pos < kGlobalCap) { r_cv[pos] = l; r_ct[pos] = (int)(col + p.sp.vocab_offset); }
+    }
+  };
+#pragma unroll
+  for (int u = 0; u < kSelPreload; ++u) {
+    const int v = tid + u * kSelThreads;
+    if (v < nvec) {
+      const T* e = reinterpret_cast<const T*>(&pre[u]);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) push(to_f32<T>(e[j]), c0 + v * VEC + j);
+    }
+  }
+  for (int v = tid + kSelPreload * kSelThreads; v < nvec; v += kSelThreads) {  // very long rows
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + c0 + v * VEC);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) push(to_f32<T>(e[j]), c0 + v * VEC + j);
+  }
+  for (int col = c0 + nvec * VEC + tid; col < c1; col += kSelThreads) push(ldl(row, col), col);  // tail / unaligned rows
+  cluster.sync();  // all candidates are in rank 0's shared memory
   if (crank != 0) return;
 
-  if (s_over) {
-    if (tid == 0) {
+  const int n = s_count;
+  if (n > kGlobalCap) {  // more ties than the buffer holds: exact full-row pass instead
+    if (p.single_shard) {
+      Best w = fullrow_resolve(row, p.V, m, p.sp.vocab_offset, s_full);
+      if (tid == 0) {
+        write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_OVERFLOW);
+        if (p.tokens) p.tokens[b] = w.t;
+        if (p.scores) p.scores[b] = w.s;
+      }
+    } else if (tid == 0) {
       write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_OVERFLOW);
-      p.rowflag[b] = 1;
-      if (!p.single_shard && p.tokens) p.tokens[b] = -1;
+      if (p.tokens) p.tokens[b] = -1;
     }
     return;
   }
-  const int n = s_total;
-  if (tid == 0) p.rowflag[b] = 0;
 
   if (p.records) {
     // shard record: the local top-k survivors (ties kept); top-p needs the union, so it waits
-    __shared__ int s_nrec;
     if (tid == 0) s_nrec = 0;
     __syncthreads();
     Cand* out = reinterpret_cast<Cand*>(p.records + (size_t)b * VQK_RECORD_BYTES + sizeof(RecordHeader));
@@ -427,123 +545,6 @@ __global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ re
   if (tid == 0) { tokens[b] = w.t; if (scores) scores[b] = w.s; }
 }
 
-// ---- exact full-row pass ---------------------------------------------------------------------------
-// k-th largest raw logit of a row by 8-bit MSB radix select on order-preserving keys.
-template <typename T>
-__device__ float radix_kth_largest(const T* row, int V, int k, unsigned int* hist /* 256 */, unsigned int* bcast /* 2 */) {
-  uint32_t prefix = 0, mask = 0;
-  int kk = k;
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-    __syncthreads();
-    for (int col = threadIdx.x; col < V; col += blockDim.x) {
-      const uint32_t key = f32_key(ldl(row, col));
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1u);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned int cum = 0;
-      int bin = 255;
-      for (; bin > 0; --bin) {
-        if (cum + hist[bin] >= (unsigned)kk) break;
-        cum += hist[bin];
-      }
-      bcast[0] = (unsigned)bin;
-      bcast[1] = cum;
-    }
-    __syncthreads();
-    prefix |= bcast[0] << shift;
-    mask |= 0xffu << shift;
-    kk -= (int)bcast[1];
-    __syncthreads();
-  }
-  return key_f32(prefix);
-}
-
-template <typename T>
-__global__ void __launch_bounds__(1024) k_fullrow(const SelectParams p) {
-  const int b = blockIdx.x, tid = threadIdx.x;
-  if (!p.rowflag[b]) return;
-  const RowMeta m = decode_row(p.sp, b);
-  const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
-  const int V = p.V;
-  __shared__ unsigned int s_hist[256];
-  __shared__ unsigned long long s_mass[256];
-  __shared__ unsigned int s_bc[2];
-  __shared__ unsigned long long s_z, s_above;
-  __shared__ Best s_redb[32];
-  __shared__ float s_redf[32];
-
-  float thr = -INFINITY;
-  if (m.top_k > 0) thr = radix_kth_largest(row, V, m.top_k, s_hist, s_bc);
-  else if (m.flags & ROW_MASK_THR) thr = m.thr;
-
-  uint32_t cut = 0;  // smallest surviving key of y; 0 keeps everything
-  if (m.top_p < 1.f) {
-    float mx = -INFINITY;
-    for (int col = tid; col < V; col += blockDim.x) {
-      const float l = ldl(row, col);
-      if (l >= thr) mx = fmaxf(mx, l / m.T);
-    }
-    mx = block_maxf(mx, s_redf);
-    if (tid == 0) { s_z = 0ull; s_above = 0ull; }
-    __syncthreads();
-    unsigned long long loc = 0;
-    for (int col = tid; col < V; col += blockDim.x) {
-      const float l = ldl(row, col);
-      if (l >= thr) loc += mass_of(l / m.T, mx);
-    }
-    atomicAdd(&s_z, loc);
-    __syncthreads();
-    const double target = (double)m.top_p * (double)s_z;
-    uint32_t prefix = 0, mask = 0;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-      for (int i = tid; i < 256; i += blockDim.x) s_mass[i] = 0ull;
-      __syncthreads();
-      for (int col = tid; col < V; col += blockDim.x) {
-        const float l = ldl(row, col);
-        if (l >= thr) {
-          const float y = l / m.T;
-          const uint32_t key = f32_key(y);
-          if ((key & mask) == prefix) atomicAdd(&s_mass[(key >> shift) & 0xff], mass_of(y, mx));
-        }
-      }
-      __syncthreads();
-      if (tid == 0) {
-        unsigned long long cum = s_above;
-        int bin = 255;
-        for (; bin > 0; --bin) {
-          if ((double)(cum + s_mass[bin]) >= target) break;
-          cum += s_mass[bin];
-        }
-        s_bc[0] = (unsigned)bin;
-        s_above = cum;
-      }
-      __syncthreads();
-      prefix |= s_bc[0] << shift;
-      mask |= 0xffu << shift;
-      __syncthreads();
-    }
-    cut = prefix;
-  }
-
-  Best best{-INFINITY, 0x7fffffff};
-  for (int col = tid; col < V; col += blockDim.x) {
-    const float l = ldl(row, col);
-    if (!(l >= thr)) continue;
-    const float y = l / m.T;
-    if (f32_key(y) < cut) continue;
-    const int tok = (int)(col + p.sp.vocab_offset);
-    const float sc = y + gumbel_noise(m.seed, (uint32_t)tok);
-    if (better(sc, tok, best.s, best.t)) { best.s = sc; best.t = tok; }
-  }
-  best = block_best(best, s_redb);
-  if (tid == 0) {
-    if (p.tokens) p.tokens[b] = best.t;
-    if (p.scores) p.scores[b] = best.s;
-  }
-}
-
 template <typename T>
 __global__ void __launch_bounds__(1024) k_topk_threshold(const T* __restrict__ logits, long long ld, int V,
                                                         const int32_t* __restrict__ top_k, float* __restrict__ thr) {
@@ -581,14 +582,7 @@ int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V,
 int launch_select(const SelectParams& p, cudaStream_t st) {
   if (p.B == 0) return VQK_OK;
   dim3 grid(kClusterSize, (unsigned)p.B);
-  VQK_DISPATCH_DTYPE(p.dtype, (k_select<T><<<grid, 256, 0, st>>>(p)));
-  VQK_LAUNCH_CHECK();
-  return VQK_OK;
-}
-
-int launch_fullrow(const SelectParams& p, cudaStream_t st) {
-  if (p.B == 0) return VQK_OK;
-  VQK_DISPATCH_DTYPE(p.dtype, (k_fullrow<T><<<(unsigned)p.B, 1024, 0, st>>>(p)));
+  VQK_DISPATCH_DTYPE(p.dtype, (k_select<T><<<grid, kSelThreads, 0, st>>>(p)));
   VQK_LAUNCH_CHECK();
   return VQK_OK;
 }
