@@ -238,8 +238,15 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
       p.part_score = ws.part_score + (size_t)b0 * nslices;
       p.part_token = ws.part_token + (size_t)b0 * nslices;
       p.nslices = nslices;
-      p.cand_logits = ws.cand + (size_t)b0 * ws.ld_cand;
-      p.ld_cand = ws.ld_cand;
+      // rows that take the candidate path need their fp16 logits in memory: the caller's logits
+      // buffer when there is one, scratch otherwise
+      if (logits) {
+        p.cand_logits = p.logits;
+        p.ld_cand = ld_logits;
+      } else {
+        p.cand_logits = ws.cand + (size_t)b0 * ws.ld_cand;
+        p.ld_cand = ws.ld_cand;
+      }
     }
     rc = use_umma ? launch_lm_head_umma(mode, p, sms, st)
          : use_tma ? launch_lm_head_tma(mode, p, sms, st)
@@ -250,7 +257,7 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   if (!sp) return VQK_OK;
 
   SelectParams s{};
-  s.logits = ws.cand; s.dtype = VQK_F16; s.ld = ws.ld_cand;
+  s.logits = logits ? logits : (void*)ws.cand; s.dtype = VQK_F16; s.ld = logits ? ld_logits : ws.ld_cand;
   s.V = (int)h->V; s.B = (int)B; s.sp = sd;
   s.slice_max = ws.slice_max; s.part_score = ws.part_score; s.part_token = ws.part_token; s.nslices = nslices;
   s.records = (uint8_t*)records; s.tokens = (long long*)tokens; s.scores = scores;

@@ -113,7 +113,8 @@ struct Geometry {
 __host__ __device__ inline Geometry geometry(int bn) {
   Geometry g;
   g.stage_bytes = BM * BK + bn * BK;
-  const size_t fixed = 1024 /* alignment slack */ + 256 /* barriers */ + (size_t)bn * sizeof(RowMeta);
+  const size_t fixed = 1024 /* alignment slack */ + 256 /* barriers */ + (size_t)bn * sizeof(RowMeta) +
+                       (size_t)12 * bn * sizeof(int) /* sampler state */;
   const size_t limit = 227 * 1024;
   int s = (int)((limit - fixed) / g.stage_bytes);
   g.stages = s > kMaxStages ? kMaxStages : s;
@@ -135,7 +136,6 @@ template <int MODE, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB) {
   constexpr bool INT8 = (MODE == VQK_MODE_W8A8);
-  constexpr int NSLOT = (BN + 31) / 32;  // batch columns a lane keeps sampler state for
   constexpr uint32_t TCOLS = (2 * BN <= 32) ? 32u : (uint32_t)(2 * BN);  // power of two for BN in {16..256}
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -149,6 +149,7 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   RowMeta* meta = reinterpret_cast<RowMeta*>(bars + 32);
+  int* sstate = reinterpret_cast<int*>(meta + BN);  // [4 warps][3][BN] sampler state of the epilogue warps
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int V = p.V, B = p.B;
@@ -225,12 +226,17 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
     }
   } else {
     // ================================ epilogue =========================================
+    // Compact by design: a runtime loop over 16-column chunks (the fully unrolled form of a
+    // 256-column epilogue does not fit the instruction cache and ran 10x slower than the MMAs).
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    int smax_key[NSLOT], best_key[NSLOT], best_tok[NSLOT];
-#pragma unroll
-    for (int i = 0; i < NSLOT; ++i) { smax_key[i] = ordered_key(-INFINITY); best_key[i] = ordered_key(-INFINITY); best_tok[i] = 0x7fffffff; }
+    int* st_max = sstate + (size_t)(q * 3 + 0) * BN;   // per warp, per batch column: slice maximum (ordered key)
+    int* st_key = sstate + (size_t)(q * 3 + 1) * BN;   // best Gumbel score (ordered key)
+    int* st_tok = sstate + (size_t)(q * 3 + 2) * BN;   // its local token id
+    for (int b = lane; b < BN; b += 32) { st_max[b] = ordered_key(-INFINITY); st_key[b] = (int)0x80000000; st_tok[b] = 0x7fffffff; }
+    __syncwarp();
     float xs_w8a8 = 1.f;
     if constexpr (INT8) xs_w8a8 = *reinterpret_cast<const float*>(p.xscale);
+    const int nchunk = (B + 15) / 16;
 
     int tcount = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
@@ -238,71 +244,137 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
       const uint32_t tph = (uint32_t)(tcount >> 1) & 1u;
       const int row = tile * BM + q * 32 + lane;
       const bool rok = row < V;
-      float rs = 1.f, bias = 0.f;
-      if (rok) {
-        rs = INT8 ? reinterpret_cast<const float*>(p.wscale)[row] : __half2float(reinterpret_cast<const __half*>(p.wscale)[row]);
-        if (p.bias) bias = __half2float(p.bias[row]);
-      }
+      const int rowc = rok ? row : V - 1;  // clamped: out-of-range lanes write nothing
+      float rs = INT8 ? reinterpret_cast<const float*>(p.wscale)[rowc] : __half2float(reinterpret_cast<const __half*>(p.wscale)[rowc]);
+      if constexpr (INT8) rs = rs;  // scale order handled below
+      const float bias = p.bias ? __half2float(p.bias[rowc]) : 0.f;
       if (!mbar_wait_warp(&tfull[buf], tph, abort_flag)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-#pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (c0 >= B) break;  // warp-uniform: padded batch columns carry nothing
+      for (int ch = 0; ch < nchunk; ++ch) {
+        const int c0 = ch * 16;
         uint32_t r[16];
         tmem_ld16(taddr + (uint32_t)c0, r);
+        // which of the 16 columns take the candidate path / exist at all
+        int myflags = 0;
+        if (lane < 16 && c0 + lane < B && p.do_sample) myflags = meta[c0 + lane].flags | 0x100;
+        const unsigned candmask = __ballot_sync(0xffffffffu, (myflags & ROW_CAND) != 0);
+        const unsigned livemask = __ballot_sync(0xffffffffu, (myflags & 0x100) != 0);
+        __half* lp = p.logits ? p.logits + (long long)c0 * p.ld_logits + rowc : nullptr;
+        __half* cp = p.cand_logits + (long long)c0 * p.ld_cand + rowc;
+        int mine_max = ordered_key(-INFINITY);
         tmem_ld_wait();
+        if (!p.bias && c0 + 16 <= B && (!p.do_sample || (candmask & 0xffffu) == 0xffffu)) {
+          // Fast path (all 16 columns exist and take the candidate path, or no sampling at all):
+          // packed fp16 conversion, one store per column, and the 32-row maximum of every column
+          // by a half2 butterfly over the warp instead of sixteen warp reductions.
+          __half2 h2[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float v0, v1;
+            if constexpr (INT8) {
+              v0 = ((float)(int)r[2 * i] * rs) * xs_w8a8;
+              v1 = ((float)(int)r[2 * i + 1] * rs) * xs_w8a8;
+            } else {
+              v0 = __uint_as_float(r[2 * i]) * rs;
+              v1 = __uint_as_float(r[2 * i + 1]) * rs;
+            }
+            h2[i] = __floats2half2_rn(v0, v1);
+          }
+          if (rok) {
+            __half* dst = cp;
+            long long ldd = p.ld_cand;
+            if (!p.do_sample) { dst = lp; ldd = p.ld_logits; }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              dst[(long long)(2 * i) * ldd] = __low2half(h2[i]);
+              dst[(long long)(2 * i + 1) * ldd] = __high2half(h2[i]);
+            }
+            if (p.do_sample && lp && lp != cp) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                lp[(long long)(2 * i) * p.ld_logits] = __low2half(h2[i]);
+                lp[(long long)(2 * i + 1) * p.ld_logits] = __high2half(h2[i]);
+              }
+            }
+          }
+          if (p.do_sample) {
+            const __half2 ninf = __float2half2_rn(-INFINITY);
+            __half2 a[4], bq[2], c;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h2[i] = rok ? h2[i] : ninf;
+            const bool up16 = lane & 16, up8 = lane & 8, up4 = lane & 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const __half2 send = up16 ? h2[i] : h2[i + 4], keep = up16 ? h2[i + 4] : h2[i];
+              a[i] = __hmax2(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const __half2 send = up8 ? a[i] : a[i + 2], keep = up8 ? a[i + 2] : a[i];
+              bq[i] = __hmax2(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+            }
+            {
+              const __half2 send = up4 ? bq[0] : bq[1], keep = up4 ? bq[1] : bq[0];
+              c = __hmax2(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+            }
+            c = __hmax2(c, __shfl_xor_sync(0xffffffffu, c, 2));
+            c = __hmax2(c, __shfl_xor_sync(0xffffffffu, c, 1));
+            if ((lane & 3) == 0) {  // this lane group holds the column pair selected by lane bits 4, 3, 2
+              const int pair = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+              const int k0 = ordered_key(__low2float(c)), k1 = ordered_key(__high2float(c));
+              st_max[c0 + 2 * pair] = max(st_max[c0 + 2 * pair], k0);
+              st_max[c0 + 2 * pair + 1] = max(st_max[c0 + 2 * pair + 1], k1);
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int b = c0 + j;
-          if (b < B) {
-            float v;
-            if constexpr (INT8) v = ((float)(int)r[j] * rs) * xs_w8a8;  // reference _kernels.py:471, left to right
-            else v = __uint_as_float(r[j]) * rs;
-            __half h = __float2half_rn(v);
-            if (p.bias) h = __float2half_rn(__half2float(h) + bias);
-            if (rok && p.logits) p.logits[(long long)b * p.ld_logits + row] = h;
-            if (p.do_sample) {
-              const RowMeta m = meta[b];
+          float v;
+          if constexpr (INT8) v = ((float)(int)r[j] * rs) * xs_w8a8;  // reference _kernels.py:471, left to right
+          else v = __uint_as_float(r[j]) * rs;
+          __half h = __float2half_rn(v);
+          if (p.bias) h = __float2half_rn(__half2float(h) + bias);
+          if (c0 + j < B) {  // warp-uniform
+            if (lp && rok) lp[(long long)j * p.ld_logits] = h;
+            if (candmask & (1u << j)) {
+              if (rok) cp[(long long)j * p.ld_cand] = h;
+              const int mk = __reduce_max_sync(0xffffffffu, rok ? ordered_key(__half2float(h)) : ordered_key(-INFINITY));
+              if (lane == j) mine_max = mk;
+            } else if (livemask & (1u << j)) {
+              const RowMeta m = meta[c0 + j];
               const float l = __half2float(h);
-              if (m.flags & ROW_CAND) {
-                if (rok) p.cand_logits[(long long)b * p.ld_cand + row] = h;
-                const int mk = __reduce_max_sync(0xffffffffu, rok ? ordered_key(l) : ordered_key(-INFINITY));
-                if (lane == (b & 31)) smax_key[b >> 5] = max(smax_key[b >> 5], mk);
-              } else {
-                float sc = l;
-                if (!(m.flags & ROW_GREEDY)) {
-                  sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(row + p.sp.vocab_offset));
-                  if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
-                }
-                const int key = rok ? ordered_key(sc) : (int)0x80000000;
-                const int mk = __reduce_max_sync(0xffffffffu, key);
-                const unsigned eq = __ballot_sync(0xffffffffu, key == mk);
-                const int tok = tile * BM + q * 32 + (__ffs(eq) - 1);  // lowest row among equal scores
-                if (lane == (b & 31)) {
-                  const int slot = b >> 5;
-                  if (mk > best_key[slot] || (mk == best_key[slot] && tok < best_tok[slot])) { best_key[slot] = mk; best_tok[slot] = tok; }
-                }
+              float sc = l;
+              if (!(m.flags & ROW_GREEDY)) {
+                sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(row + p.sp.vocab_offset));
+                if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
+              }
+              const int key = rok ? ordered_key(sc) : (int)0x80000000;
+              const int mk = __reduce_max_sync(0xffffffffu, key);
+              const unsigned eq = __ballot_sync(0xffffffffu, key == mk);
+              const int tok = tile * BM + q * 32 + (__ffs(eq) - 1);  // lowest row among equal scores
+              if (lane == j && (mk > st_key[c0 + j] || (mk == st_key[c0 + j] && tok < st_tok[c0 + j]))) {
+                st_key[c0 + j] = mk;
+                st_tok[c0 + j] = tok;
               }
             }
           }
         }
+        if (lane < 16 && (candmask & (1u << lane))) st_max[c0 + lane] = max(st_max[c0 + lane], mine_max);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);
     }
+    __syncwarp();
     if (p.do_sample) {
       const int slice = blockIdx.x * 4 + q;
-#pragma unroll
-      for (int i = 0; i < NSLOT; ++i) {
-        const int b = i * 32 + lane;
-        if (b < B) {
-          const long long o = (long long)b * p.nslices + slice;
-          p.slice_max[o] = key_to_float(smax_key[i]);
-          p.part_score[o] = best_key[i] == (int)0x80000000 ? -INFINITY : key_to_float(best_key[i]);
-          p.part_token[o] = best_tok[i];
-        }
+      for (int b = lane; b < B; b += 32) {
+        const long long o = (long long)b * p.nslices + slice;
+        p.slice_max[o] = key_to_float(st_max[b]);
+        p.part_score[o] = st_key[b] == (int)0x80000000 ? -INFINITY : key_to_float(st_key[b]);
+        p.part_token[o] = st_tok[b];
       }
     }
   }

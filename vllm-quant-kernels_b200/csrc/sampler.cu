@@ -302,6 +302,52 @@ __device__ Best fullrow_resolve(const T* row, int V, const RowMeta& m, long long
   return block_best(best, s_redb);
 }
 
+// k-th largest of n floats in shared memory (n >= k >= 1): 8-bit MSB radix select, one warp
+// scans each 256-bin histogram.  Called by the whole block; result in every thread.
+__device__ float smem_kth_largest(const float* v, int n, int k, unsigned int* hist /* 256 */, unsigned int* bc /* 2 */) {
+  uint32_t prefix = 0, mask = 0;
+  int kk = k;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const uint32_t key = f32_key(v[i]);
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      unsigned int h[8], tot = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { h[j] = hist[lane * 8 + j]; tot += h[j]; }
+      // suffix sum over lanes: above = number of keys in bins owned by higher lanes
+      unsigned int incl = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        unsigned int t = __shfl_down_sync(0xffffffffu, incl, o);
+        if (lane + o < 32) incl += t;
+      }
+      const unsigned int above = incl - tot;
+      if (above < (unsigned)kk && incl >= (unsigned)kk) {  // exactly one lane
+        unsigned int cum = above;
+        int bin = 7;
+        for (; bin > 0; --bin) {
+          if (cum + h[bin] >= (unsigned)kk) break;
+          cum += h[bin];
+        }
+        bc[0] = (unsigned)(lane * 8 + bin);
+        bc[1] = cum;
+      }
+    }
+    __syncthreads();
+    prefix |= bc[0] << shift;
+    mask |= 0xffu << shift;
+    kk -= (int)bc[1];
+    __syncthreads();
+  }
+  return key_f32(prefix);
+}
+
 // ---- pass 2: one cluster per row -----------------------------------------------------------------
 // Two cluster barriers per row.  Every CTA first puts its share of the row in flight (16-byte
 // loads into registers), then the cluster rank-counts the slice maxima for tau while those loads
@@ -327,8 +373,6 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kSelThrea
   __shared__ Best s_redb[32];
   __shared__ float s_redf[32];
   __shared__ unsigned long long s_z;
-  __shared__ float s_tau_slot[kClusterSize];  // rank 0's copy is the one everybody reads
-  __shared__ float s_tau_local;
   __shared__ int s_count;
   __shared__ int s_nrec;
   __shared__ FullRowScratch s_full;
@@ -383,35 +427,16 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kSelThrea
     pre[u] = v < nvec ? *reinterpret_cast<const uint4*>(row + c0 + v * VEC) : make_uint4(0, 0, 0, 0);
   }
 
-  // ---- tau: k-th largest slice maximum, rank counting split over the cluster --------------
-  if (tid == 0) { s_count = 0; s_tau_local = -INFINITY; }
+  // ---- tau: k-th largest slice maximum, radix select in shared memory (every CTA for itself) ---
+  if (tid == 0) s_count = 0;
   float tau = m.thr;
   if (m.top_k > 0) {
     const int ns = p.nslices;
     for (int s = tid; s < ns; s += blockDim.x) s_sm[s] = p.slice_max[(long long)b * ns + s];
     __syncthreads();
-    const int share = (ns + kClusterSize - 1) / kClusterSize;
-    const int i0 = crank * share, i1 = min(ns, i0 + share);
-    for (int i = i0 + warp; i < i1; i += kSelThreads / 32) {
-      const float vi = s_sm[i];
-      int cnt = 0;
-      for (int j = lane; j < ns; j += 32) {
-        const float vj = s_sm[j];
-        cnt += (vj > vi) || (vj == vi && j < i);
-      }
-      cnt = __reduce_add_sync(0xffffffffu, cnt);
-      if (cnt == m.top_k - 1 && lane == 0) s_tau_local = vi;  // ranks are unique: at most one writer in the cluster
-    }
-    __syncthreads();
-    if (tid == 0) *cluster.map_shared_rank(&s_tau_slot[crank], 0) = s_tau_local;
-    cluster.sync();  // slots and rank 0's counter are set
-    const float* slots = cluster.map_shared_rank(&s_tau_slot[0], 0);
-    tau = -INFINITY;
-#pragma unroll
-    for (int r = 0; r < kClusterSize; ++r) tau = fmaxf(tau, slots[r]);
-  } else {
-    cluster.sync();
+    tau = smem_kth_largest(s_sm, ns, m.top_k, s_full.hist, s_full.bc);
   }
+  cluster.sync();  // rank 0's candidate counter is zero before anybody pushes
 
   // ---- candidates >= tau go to rank 0 ---------------------------------------------------------
   int* r_count = cluster.map_shared_rank(&s_count, 0);
