@@ -169,6 +169,26 @@ int vqk_sample(const void* logits, int dtype, int64_t B, int64_t V, int64_t ld,
                const vqk_sample_params* sp, int64_t* tokens, float* scores, void* records,
                void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The same sampler for callers that must not allocate (no counterpart in the reference).
+ * Some hosts cannot call cudaMalloc where they sample: an engine that measured its memory
+ * once and handed every remaining byte to its KV cache has nothing left to ask for, and a
+ * call made between the begin and end of a stream capture may not allocate at all.  This
+ * entry point takes no workspace and makes no allocation of any kind: its scratch (the
+ * per-slice arrays vqk_sample keeps in the caller's workspace) is a fixed array inside the
+ * library, VQK_STATIC_SCRATCH_BYTES per GPU, held from library load until process exit.
+ * Limits: B <= VQK_STATIC_MAX_ROWS and V <= VQK_STATIC_MAX_VOCAB, else VQK_ERR_TOO_LARGE;
+ * single shard only (vocab_offset 0, vocab_total == V); tokens are required.
+ * The first call on each device looks up the array's device address; make that first
+ * call before any stream capture begins on that device.
+ * All calls share the one array: the library rewrites every element it later reads, so
+ * nothing carries over between calls, but two calls whose kernels overlap on the GPU
+ * (different streams) race on it - serialise them. */
+#define VQK_STATIC_MAX_ROWS 64
+#define VQK_STATIC_MAX_VOCAB 262144
+#define VQK_STATIC_SCRATCH_BYTES (3 * VQK_STATIC_MAX_ROWS * (VQK_STATIC_MAX_VOCAB / 256) * 4)
+int vqk_sample_static(const void* logits, int dtype, int64_t B, int64_t V, int64_t ld,
+                      const vqk_sample_params* sp, int64_t* tokens, float* scores, void* stream);
+
 /* Merge all-gathered records [G][B] into final tokens; every rank computes the same
  * answer.  Higher score wins, equal scores go to the lower token id (the first-index
  * rule of _sampler_kernels.py:116-120,180-181).  Rows whose records carry an overflow

@@ -113,7 +113,8 @@ extern "C" const char* vqk_strerror(int s) {
     case VQK_ERR_WORKSPACE: return "workspace missing or too small";
     case VQK_ERR_ARCH: return "device is not sm_100 (B200); there is no fallback path";
     case VQK_ERR_COMM: return "NCCL unavailable or collective failed";
-    case VQK_ERR_TOO_LARGE: return "size exceeds a fixed maximum";
+    case VQK_ERR_TOO_LARGE:
+      return "size exceeds a fixed maximum (vqk_sample_static: at most 64 rows of at most 262144 columns)";
   }
   return "unknown status";
 }
@@ -316,6 +317,19 @@ extern "C" int vqk_sample(const void* logits, int dtype, int64_t B, int64_t V, i
   s.records = (uint8_t*)records; s.tokens = (long long*)tokens; s.scores = scores;
   s.single_shard = tokens ? 1 : 0;
   return launch_select(s, st);
+}
+
+extern "C" int vqk_sample_static(const void* logits, int dtype, int64_t B, int64_t V, int64_t ld,
+                                 const vqk_sample_params* sp, int64_t* tokens, float* scores, void* stream) {
+  if (!logits || !sp || !tokens || B < 0 || V <= 0 || ld < V) return VQK_ERR_INVALID;
+  if (dtype < VQK_F16 || dtype > VQK_F32) return VQK_ERR_INVALID;
+  if (sp->temperature && !sp->seeds) return VQK_ERR_INVALID;
+  if (B > VQK_STATIC_MAX_ROWS || V > VQK_STATIC_MAX_VOCAB) return VQK_ERR_TOO_LARGE;
+  if (sp->vocab_total != V || sp->vocab_offset != 0) return VQK_ERR_INVALID;
+  if (B == 0) return VQK_OK;
+  int rc = require_sm100();
+  if (rc) return rc;
+  return sample_static(logits, dtype, ld, (int)B, (int)V, to_dev(sp), (long long*)tokens, scores, (cudaStream_t)stream);
 }
 
 extern "C" int vqk_sample_finalize(const void* records, int G, int64_t B, const vqk_sample_params* sp, int64_t* tokens,

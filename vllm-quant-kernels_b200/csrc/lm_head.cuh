@@ -73,6 +73,9 @@ int launch_select(const SelectParams& p, cudaStream_t st);
 // merge gathered records
 int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, long long* tokens, float* scores,
                     cudaStream_t st);
+// sampler on materialised logits with its scratch in a static device array (no allocation)
+int sample_static(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, long long* tokens,
+                  float* scores, cudaStream_t st);
 int launch_topk_threshold(const void* logits, int dtype, long long ld, int B, int V, const int32_t* top_k, float* thr,
                           cudaStream_t st);
 

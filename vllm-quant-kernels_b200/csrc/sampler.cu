@@ -628,4 +628,44 @@ int launch_topk_threshold(const void* logits, int dtype, long long ld, int B, in
   return VQK_OK;
 }
 
+
+// ---- sampler entry that allocates nothing ---------------------------------------------------------
+// Scratch for vqk_sample_static lives in this file-scope device array instead of a caller
+// workspace.  Every GPU that loads the library keeps these bytes until the process exits.
+// In host code the array's NAME is only a host-side stand-in: the device address is fetched
+// once per device with cudaGetSymbolAddress (with that device current) and that pointer is
+// what the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[VQK_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_ptr[64];  // per device, filled on the first call there
+
+int sample_static(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, long long* tokens,
+                  float* scores, cudaStream_t st) {
+  if (B > VQK_STATIC_MAX_ROWS || V > VQK_STATIC_MAX_VOCAB) return VQK_ERR_TOO_LARGE;
+  int dev = 0;
+  VQK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
+  if (!g_static_scratch_ptr[dev]) {  // set-up: once per device, with that device current
+    void* ptr = nullptr;
+    VQK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  const int nslices = slice_pass_nslices(V);
+  // three [B][nslices] arrays, each starting on a 256-byte boundary; all of them are fully
+  // rewritten by the first pass before the second pass reads them, so nothing needs clearing
+  const size_t each = (((size_t)B * nslices * sizeof(float)) + 255) & ~(size_t)255;
+  if (3 * each > (size_t)VQK_STATIC_SCRATCH_BYTES) return VQK_ERR_TOO_LARGE;
+  unsigned char* base = static_cast<unsigned char*>(g_static_scratch_ptr[dev]);
+  float* slice_max = reinterpret_cast<float*>(base);
+  float* part_score = reinterpret_cast<float*>(base + each);
+  int* part_token = reinterpret_cast<int*>(base + 2 * each);
+  int rc = launch_slice_pass(logits, dtype, ld, B, V, sp, slice_max, part_score, part_token, nslices, st);
+  if (rc) return rc;
+  SelectParams s{};
+  s.logits = logits; s.dtype = dtype; s.ld = ld; s.V = V; s.B = B; s.sp = sp;
+  s.slice_max = slice_max; s.part_score = part_score; s.part_token = part_token; s.nslices = nslices;
+  s.records = nullptr; s.tokens = tokens; s.scores = scores;
+  s.single_shard = 1;
+  return launch_select(s, st);
+}
+
 }  // namespace vqk

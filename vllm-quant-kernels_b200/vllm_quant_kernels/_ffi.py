@@ -18,13 +18,15 @@ F16, BF16, F32 = range(3)
 RECORD_BYTES = 1024
 RECORD_CAP = 126
 COMM_ID_BYTES = 128
+STATIC_MAX_ROWS = 64
+STATIC_MAX_VOCAB = 262144
 
 # every symbol include/vqk.h declares
 SYMBOLS = (
     "vqk_version", "vqk_strerror", "vqk_last_cuda_error", "vqk_device_error", "vqk_quantize_weight", "vqk_quantize_act",
     "vqk_lm_head_create", "vqk_lm_head_destroy", "vqk_lm_head_workspace_bytes", "vqk_lm_head_forward",
     "vqk_lm_head_set_kernel_events",
-    "vqk_sample_workspace_bytes", "vqk_sample", "vqk_sample_finalize", "vqk_topk_threshold",
+    "vqk_sample_workspace_bytes", "vqk_sample", "vqk_sample_static", "vqk_sample_finalize", "vqk_topk_threshold",
     "vqk_comm_unique_id", "vqk_comm_create", "vqk_comm_allgather", "vqk_comm_destroy",
 )
 
@@ -74,6 +76,8 @@ def lib() -> ctypes.CDLL:
     L.vqk_sample_workspace_bytes.argtypes = [c_int64, c_int64]
     L.vqk_sample.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int64, POINTER(SampleParams), c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int64, c_void_p]
+    L.vqk_sample_static.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int64, POINTER(SampleParams), c_void_p, c_void_p,
+                                    c_void_p]
     L.vqk_sample_finalize.argtypes = [c_void_p, c_int, c_int64, POINTER(SampleParams), c_void_p, c_void_p, c_void_p]
     L.vqk_topk_threshold.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]
     L.vqk_comm_unique_id.argtypes = [c_void_p]

@@ -319,3 +319,33 @@ def topk_threshold(logits: torch.Tensor, top_k: torch.Tensor) -> torch.Tensor:
             _ffi.check(_ffi.lib().vqk_topk_threshold(logits.data_ptr(), _DT[logits.dtype], B, V, logits.stride(0),
                                                      k.data_ptr(), thr.data_ptr(), _stream(logits)))
     return thr
+
+
+def sample_logits_static(logits: torch.Tensor, sp: SamplingArgs):
+    """`sample_logits` for callers that must not allocate device memory inside the call:
+    the library keeps the sampler's scratch in a fixed array of its own, so no workspace is
+    requested from torch (or anyone).  The two output tensors are still the caller's; pass
+    `out=(tokens, scores)`-style pre-allocated tensors through `sample_logits_static_into`
+    to avoid even those.  Limits: at most 64 rows of at most 262144 columns, single shard.
+    Calls share the scratch, so do not overlap two of them on different streams; make the
+    first call on a device before any CUDA-graph capture starts there."""
+    B = logits.shape[0]
+    tokens = torch.empty(B, dtype=torch.int64, device=logits.device)
+    scores = torch.empty(B, dtype=torch.float32, device=logits.device)
+    sample_logits_static_into(logits, sp, tokens, scores)
+    return tokens, scores
+
+
+def sample_logits_static_into(logits: torch.Tensor, sp: SamplingArgs, tokens: torch.Tensor,
+                              scores: Optional[torch.Tensor] = None) -> None:
+    """Allocation-free form: every buffer, outputs included, comes from the caller."""
+    _require_cuda(logits, "logits")
+    assert logits.dim() == 2 and logits.dtype in _DT and logits.stride(1) == 1
+    B, V = logits.shape
+    assert tokens.dtype == torch.int64 and tokens.shape == (B,) and tokens.is_contiguous()
+    if scores is not None:
+        assert scores.dtype == torch.float32 and scores.shape == (B,) and scores.is_contiguous()
+    spc = sp.to_c(B, V)
+    with torch.cuda.device(logits.device):
+        _ffi.check(_ffi.lib().vqk_sample_static(logits.data_ptr(), _DT[logits.dtype], B, V, logits.stride(0),
+                                                ctypes.byref(spc), tokens.data_ptr(), _ptr(scores), _stream(logits)))
