@@ -1,0 +1,63 @@
+"""Worker of tests/test_gpu_multi.py (launched by torch.distributed.run, one rank per GPU).
+
+Every rank builds the same seeded weights, keeps its vocab slice, and runs the sharded step
+twice: once exchanging records through libvqk's own NCCL communicator, once through
+torch.distributed.  Rank 0 also runs the unsharded step; all results must be identical."""
+
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "vllm-quant-kernels_b200"))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+
+def main():
+    from vllm_quant_kernels import _lmhead as LH
+    from vllm_quant_kernels._dist import VocabShardedLMHead, VqkComm, shard_bounds
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    V, H, B = 16 * 8 * 97, 1024, 6
+    g = torch.Generator().manual_seed(7)
+    std = torch.exp(torch.empty(V).uniform_(np.log(0.03), np.log(0.18), generator=g))
+    w = (torch.randn(V, H, generator=g) * std[:, None]).clamp_(-0.76, 0.76).half().to(dev)
+    x = torch.randn(B, H, generator=g).half().to(dev)
+    rng = np.random.default_rng(3)
+    T = rng.uniform(0.5, 1.5, B).astype(np.float32)
+    T[0] = 0.0
+    seeds = rng.integers(0, 2**31 - 1, B).astype(np.int32)
+
+    def args(**kw):
+        t = lambda a, dt: None if a is None else torch.from_numpy(np.asarray(a)).to(dt).to(dev)
+        return LH.SamplingArgs(t(T, torch.float32), t(seeds, torch.int32), t(kw.get("top_k"), torch.int32),
+                               t(kw.get("top_p"), torch.float32), None, 0, V)
+
+    comm = VqkComm(rank, world)
+    a, b = shard_bounds(V, world, rank)
+    for mode in ("int8", "mxfp4"):
+        q, s = LH.quantize_weight(mode, w)
+        full = LH.LMHeadShard(mode, q, s)
+        mine = LH.LMHeadShard(mode, q[a:b].contiguous(), s[a:b].contiguous())
+        for kw in (dict(), dict(top_k=np.full(B, 50, np.int32), top_p=np.full(B, 0.9, np.float32))):
+            sp = args(**kw)
+            ref_tok, ref_sc = full.sample(x, sp)
+            for c in (comm, None):
+                tok, sc = VocabShardedLMHead(mine, a, V, comm=c).step(x, sp)
+                torch.cuda.synchronize()
+                assert torch.equal(tok, ref_tok), (rank, mode, list(kw), tok.tolist(), ref_tok.tolist())
+                assert torch.equal(sc, ref_sc)
+    dist.barrier()
+    comm.close()
+    if rank == 0:
+        print("MULTI_GPU_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
