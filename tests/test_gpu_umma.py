@@ -76,3 +76,25 @@ def test_umma_fused_sampling(mode, B, monkeypatch):
         assert torch.equal(tok, tok3)
     ref_logits = _oracle(mode, x, w)
     assert OLM.rel_l2(t2n(logits), ref_logits) <= REL_L2
+
+
+@pytest.mark.parametrize("mode", ["mxfp8", "mxfp4"])
+@pytest.mark.parametrize("B,H", [(1, 1024), (16, 3072), (33, 1024), (100, 2048), (128, 1024), (200, 1024)])
+def test_umma_block_scaled_logits_vs_oracle(mode, B, H, monkeypatch):
+    """Block-scaled tensor-core kernel (scale factors through TMEM, packed E2M1 expanded by the
+    TMA unit) against the oracle and against the register-streaming kernel."""
+    from vllm_quant_kernels import _ffi
+    V = 16 * 333
+    w = make_weight(V, H, seed=H + B)
+    x = make_act(B, H, seed=B)
+    q, s = L().quantize_weight(mode, w)
+    shard = L().LMHeadShard(mode, q, s)
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "umma")
+    got = t2n(shard.logits(x))
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "stream")
+    got_stream = t2n(shard.logits(x))
+    monkeypatch.delenv("VQK_LM_HEAD_KERNEL", raising=False)
+    assert _ffi.lib().vqk_device_error() == 0
+    ref = _oracle(mode, x, w)
+    assert OLM.rel_l2(got_stream, ref) <= REL_L2
+    assert OLM.rel_l2(got, ref) <= REL_L2, (mode, B, H, OLM.rel_l2(got, ref))

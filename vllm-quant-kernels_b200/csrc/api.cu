@@ -122,8 +122,8 @@ extern "C" const char* vqk_strerror(int s) {
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int vqk_device_error(void) {
-  const int a = stream_error_flag(), b = umma_error_flag();
-  return (a < 0 || b < 0) ? -1 : (a | b);
+  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag();
+  return (a < 0 || b < 0 || c < 0) ? -1 : (a | b | c);
 }
 
 extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
@@ -194,7 +194,8 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   const bool want_stream = kenv && !strcmp(kenv, "stream");
   int maxcols = want_tma ? tma_max_cols(mode, (int)h->H) : 0;
   const bool use_tma = want_tma && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
-  const int umma_cols = umma_max_cols(mode, (int)h->H);
+  const bool mx_mode = (mode == VQK_MODE_MXFP8 || mode == VQK_MODE_MXFP4);
+  const int umma_cols = mx_mode ? umma_mx_max_cols(mode, (int)h->H) : umma_max_cols(mode, (int)h->H);
   const bool use_umma = !use_tma && !want_stream && umma_cols > 0 && (want_umma || B > kUmmaMinBatch);
   if (use_umma) maxcols = umma_cols;
   else if (!use_tma) maxcols = stream_max_cols(mode, (int)h->H);
@@ -249,7 +250,7 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
         p.ld_cand = ws.ld_cand;
       }
     }
-    rc = use_umma ? launch_lm_head_umma(mode, p, sms, st)
+    rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
          : use_tma ? launch_lm_head_tma(mode, p, sms, st)
                    : launch_lm_head_stream(mode, p, sms, st);
     if (rc) return rc;

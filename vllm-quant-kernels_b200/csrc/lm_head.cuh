@@ -40,6 +40,10 @@ int stream_error_flag();               // 1 if a bounded wait inside the kernel 
 int umma_max_cols(int mode, int K);    // 256, or 0 when the mode / shape is not covered
 int launch_lm_head_umma(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
 int umma_error_flag();
+// lm_head_umma_mx.cu: block-scaled tcgen05 kernel (MXFP8, MXFP4; K % 128 == 0; up to 128 columns)
+int umma_mx_max_cols(int mode, int K);
+int launch_lm_head_umma_mx(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
+int umma_mx_error_flag();
 
 // quantize.cu
 int quantize_act_dispatch(int mode, const void* x, int dt, long long B, long long H, long long ldx, void* xq,
