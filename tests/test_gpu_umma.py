@@ -98,3 +98,86 @@ def test_umma_block_scaled_logits_vs_oracle(mode, B, H, monkeypatch):
     ref = _oracle(mode, x, w)
     assert OLM.rel_l2(got_stream, ref) <= REL_L2
     assert OLM.rel_l2(got, ref) <= REL_L2, (mode, B, H, OLM.rel_l2(got, ref))
+
+
+@pytest.mark.parametrize("mode", ["mxfp8", "mxfp4"])
+@pytest.mark.parametrize("B,H", [(4, 1024), (40, 512), (20, 384)])
+def test_umma_block_scaled_many_tiles(mode, B, H, monkeypatch):
+    """More 128-row tiles than SMs, so every CTA walks several tiles (scale hand-over between
+    tiles, accumulator double buffering), a ragged last tile, and a K with an odd number of
+    128-element blocks (H = 384: the one-block-per-stage variant)."""
+    from vllm_quant_kernels import _ffi
+    V = 128 * 450 + 40
+    w = make_weight(V, H, seed=H)
+    x = make_act(B, H, seed=B)
+    q, s = L().quantize_weight(mode, w)
+    shard = L().LMHeadShard(mode, q, s)
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "umma")
+    got = t2n(shard.logits(x))
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "stream")
+    got_stream = t2n(shard.logits(x))
+    monkeypatch.delenv("VQK_LM_HEAD_KERNEL", raising=False)
+    assert _ffi.lib().vqk_device_error() == 0
+    assert OLM.rel_l2(got, got_stream) <= REL_L2, (mode, B, H, OLM.rel_l2(got, got_stream))
+    ref = _oracle(mode, x[:2], w[:4096])
+    assert OLM.rel_l2(got[:2, :4096], ref) <= REL_L2
+
+
+@pytest.mark.parametrize("mode", ["mxfp8", "mxfp4"])
+@pytest.mark.parametrize("B", [1, 5, 8, 9, 16, 24])
+def test_umma_block_scaled_fused_sampling(mode, B, monkeypatch):
+    """Default dispatch of the block-scaled modes (decode batches: weights on the N side of the
+    MMA, 256-row tiles; larger ones: weights on the M side): fused tokens equal the sampler run
+    on the logits the kernel materialises, with and without a logits buffer, a bias, and a vocab
+    that ends inside a tile."""
+    V, H = 256 * 300 + 72, 1024
+    w = make_weight(V, H, seed=11) * 4.0
+    x = make_act(B, H, seed=B)
+    bias = make_act(1, V, seed=3)[0]
+    q, s = L().quantize_weight(mode, w)
+    shard = L().LMHeadShard(mode, q, s)
+    rng = np.random.default_rng(B)
+    T = rng.uniform(0.5, 1.5, B).astype(np.float32)
+    T[B // 2] = 0.0
+    seeds = rng.integers(0, 2**31 - 1, B).astype(np.int32)
+    monkeypatch.delenv("VQK_LM_HEAD_KERNEL", raising=False)
+    for kw in (dict(), dict(top_k=np.full(B, 50, np.int32), top_p=np.full(B, 0.9, np.float32))):
+        sp = sample_args(B, DEV, T, seeds, **kw)
+        tok, sc, logits = shard.sample(x, sp, return_logits=True)
+        tok2, sc2 = L().sample_logits(logits, sp)
+        assert torch.equal(tok, tok2) and torch.equal(sc, sc2), (mode, B, list(kw))
+        ref = OS.sample(t2n(logits).astype(np.float32), T, seeds, **kw)
+        assert_tokens_match(tok, ref, what=f"block-scaled fused {mode} {list(kw)}")
+        tok3, _ = shard.sample(x, sp)
+        assert torch.equal(tok, tok3)
+    ref_logits = _oracle(mode, x, w)
+    assert OLM.rel_l2(t2n(logits), ref_logits) <= REL_L2
+    got_b = t2n(shard.logits(x, bias))
+    assert OLM.rel_l2(got_b, _oracle(mode, x, w, bias)) <= REL_L2
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "stream")
+    got_s = t2n(shard.logits(x, bias))
+    monkeypatch.delenv("VQK_LM_HEAD_KERNEL", raising=False)
+    assert OLM.rel_l2(got_b, got_s) <= REL_L2
+
+
+@pytest.mark.parametrize("mode", ["fp8", "mxfp8", "mxfp4"])
+def test_umma_small_vocab_sampling(mode, monkeypatch):
+    """Fewer tiles than SMs: the CTAs without a tile still have to write their (empty) slice
+    records, or the sampler would read stale scratch."""
+    B, V, H = 6, 16 * 333, 1024
+    w = make_weight(V, H, seed=2) * 4.0
+    x = make_act(B, H, seed=1)
+    q, s = L().quantize_weight(mode, w)
+    shard = L().LMHeadShard(mode, q, s)
+    T = np.full(B, 0.8, np.float32)
+    T[0] = 0.0
+    seeds = np.arange(B, dtype=np.int32) + 5
+    monkeypatch.setenv("VQK_LM_HEAD_KERNEL", "umma")
+    for kw in (dict(), dict(top_k=np.full(B, 20, np.int32))):
+        sp = sample_args(B, DEV, T, seeds, **kw)
+        tok, sc, logits = shard.sample(x, sp, return_logits=True)
+        tok2, sc2 = L().sample_logits(logits, sp)
+        assert torch.equal(tok, tok2) and torch.equal(sc, sc2)
+        tok3, _ = shard.sample(x, sp)
+        assert torch.equal(tok, tok3)
+    monkeypatch.delenv("VQK_LM_HEAD_KERNEL", raising=False)

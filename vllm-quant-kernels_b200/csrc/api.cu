@@ -122,7 +122,7 @@ extern "C" const char* vqk_strerror(int s) {
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int vqk_device_error(void) {
-  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag();
+  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag() | umma_wide_error_flag();
   return (a < 0 || b < 0 || c < 0) ? -1 : (a | b | c);
 }
 
@@ -190,13 +190,16 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   // tma is the bulk-copy pipeline variant of the streaming kernel).
   const char* kenv = getenv("VQK_LM_HEAD_KERNEL");
   const bool want_tma = kenv && !strcmp(kenv, "tma");
-  const bool want_umma = kenv && !strcmp(kenv, "umma");
+  const bool want_swap = kenv && !strcmp(kenv, "umma_swap");  // tensor-core kernel with the weights on the M side
+  const bool want_umma = want_swap || (kenv && !strcmp(kenv, "umma"));
   const bool want_stream = kenv && !strcmp(kenv, "stream");
   int maxcols = want_tma ? tma_max_cols(mode, (int)h->H) : 0;
   const bool use_tma = want_tma && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
   const bool mx_mode = (mode == VQK_MODE_MXFP8 || mode == VQK_MODE_MXFP4);
   const int umma_cols = mx_mode ? umma_mx_max_cols(mode, (int)h->H) : umma_max_cols(mode, (int)h->H);
-  const bool use_umma = !use_tma && !want_stream && umma_cols > 0 && (want_umma || B > kUmmaMinBatch);
+  // the block-scaled modes take the tensor-core path at every batch size: the hardware applies
+  // the E8M0 scales, which the register kernel has to do with ALU work per element
+  const bool use_umma = !use_tma && !want_stream && umma_cols > 0 && (want_umma || mx_mode || B > kUmmaMinBatch);
   if (use_umma) maxcols = umma_cols;
   else if (!use_tma) maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
@@ -250,7 +253,9 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
         p.ld_cand = ws.ld_cand;
       }
     }
-    rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
+    const bool wide = use_umma && mx_mode && !want_swap && umma_wide_eligible(mode, p.K, p.B);
+    rc = wide ? launch_lm_head_umma_wide(mode, p, sms, st)
+         : use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
          : use_tma ? launch_lm_head_tma(mode, p, sms, st)
                    : launch_lm_head_stream(mode, p, sms, st);
     if (rc) return rc;

@@ -189,8 +189,7 @@ static int launch_one(const LmHeadParams& p, const CUtensorMap& a, const CUtenso
     VQK_CUDA(cudaFuncSetAttribute(k_lm_head_umma<MODE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)geo.total));
     configured[dev] = true;
   }
-  const int ntiles = (p.V + BM - 1) / BM;
-  k_lm_head_umma<MODE, BN><<<grid < ntiles ? grid : ntiles, kThreads, geo.total, st>>>(p, a, b);
+  k_lm_head_umma<MODE, BN><<<grid, kThreads, geo.total, st>>>(p, a, b);
   VQK_LAUNCH_CHECK();
   return VQK_OK;
 }
