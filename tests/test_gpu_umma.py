@@ -53,7 +53,7 @@ def test_umma_logits_vs_oracle(mode, B, H, monkeypatch):
 @pytest.mark.parametrize("mode", ["fp8", "w8a8"])
 @pytest.mark.parametrize("B", [24, 64, 130])
 def test_umma_fused_sampling(mode, B, monkeypatch):
-    """Default dispatch (batch > 16 -> tensor-core kernel): fused tokens equal the sampler run on
+    """Default dispatch (batch > 8 -> tensor-core kernel): fused tokens equal the sampler run on
     the logits the kernel materialises, and the oracle sampler where its margin allows."""
     V, H = 128 * 391 + 48, 1024
     w = make_weight(V, H, seed=5) * 4.0
@@ -126,10 +126,10 @@ def test_umma_block_scaled_many_tiles(mode, B, H, monkeypatch):
 @pytest.mark.parametrize("mode", ["mxfp8", "mxfp4"])
 @pytest.mark.parametrize("B", [1, 5, 8, 9, 16, 24])
 def test_umma_block_scaled_fused_sampling(mode, B, monkeypatch):
-    """Default dispatch of the block-scaled modes (decode batches: weights on the N side of the
-    MMA, 256-row tiles; larger ones: weights on the M side): fused tokens equal the sampler run
-    on the logits the kernel materialises, with and without a logits buffer, a bias, and a vocab
-    that ends inside a tile."""
+    """Default dispatch of the block-scaled modes (tensor-core kernel at every batch size, three
+    MMA pipelines per CTA for narrow batches): fused tokens equal the sampler run on the logits
+    the kernel materialises, with and without a logits buffer, a bias, and a vocab that ends
+    inside a tile."""
     V, H = 256 * 300 + 72, 1024
     w = make_weight(V, H, seed=11) * 4.0
     x = make_act(B, H, seed=B)

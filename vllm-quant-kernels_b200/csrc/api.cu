@@ -92,7 +92,7 @@ static LmHeadWs carve_lm_head(void* base, int mode, long long V, long long K, lo
 using namespace vqk;
 
 // batches above this go to the tensor-core kernel (FP8 / W8A8)
-static const int kUmmaMinBatch = 16;
+static const int kUmmaMinBatch = 8;
 
 struct vqk_lm_head {
   int mode;
@@ -122,7 +122,7 @@ extern "C" const char* vqk_strerror(int s) {
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int vqk_device_error(void) {
-  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag() | umma_wide_error_flag();
+  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag();
   return (a < 0 || b < 0 || c < 0) ? -1 : (a | b | c);
 }
 
@@ -190,8 +190,7 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   // tma is the bulk-copy pipeline variant of the streaming kernel).
   const char* kenv = getenv("VQK_LM_HEAD_KERNEL");
   const bool want_tma = kenv && !strcmp(kenv, "tma");
-  const bool want_swap = kenv && !strcmp(kenv, "umma_swap");  // tensor-core kernel with the weights on the M side
-  const bool want_umma = want_swap || (kenv && !strcmp(kenv, "umma"));
+  const bool want_umma = kenv && !strcmp(kenv, "umma");
   const bool want_stream = kenv && !strcmp(kenv, "stream");
   int maxcols = want_tma ? tma_max_cols(mode, (int)h->H) : 0;
   const bool use_tma = want_tma && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
@@ -253,9 +252,7 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
         p.ld_cand = ws.ld_cand;
       }
     }
-    const bool wide = use_umma && mx_mode && !want_swap && umma_wide_eligible(mode, p.K, p.B);
-    rc = wide ? launch_lm_head_umma_wide(mode, p, sms, st)
-         : use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
+    rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
          : use_tma ? launch_lm_head_tma(mode, p, sms, st)
                    : launch_lm_head_stream(mode, p, sms, st);
     if (rc) return rc;

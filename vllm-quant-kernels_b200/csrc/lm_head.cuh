@@ -44,10 +44,6 @@ int umma_error_flag();
 int umma_mx_max_cols(int mode, int K);
 int launch_lm_head_umma_mx(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
 int umma_mx_error_flag();
-// lm_head_umma_wide.cu: block-scaled tcgen05 kernel for decode batches (weights on the N side)
-bool umma_wide_eligible(int mode, int K, int B);
-int launch_lm_head_umma_wide(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
-int umma_wide_error_flag();
 
 // quantize.cu
 int quantize_act_dispatch(int mode, const void* x, int dt, long long B, long long H, long long ldx, void* xq,

@@ -2,62 +2,69 @@
 // the 128 vocab rows of a tile are the M side of the MMA, the (padded) batch is the N side,
 // so the weight matrix is streamed exactly once whatever the batch.
 //
-//   warp 0      TMA producer: per 128-byte K block one 2-D tensor copy of the weight tile
-//               (128 rows x 128 B, 128-byte swizzle) and one of the activations (BN rows x 128 B)
-//               into a ring of shared-memory stages, completion on an mbarrier.
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (kind::i8 for W8A8, kind::f8f6f4 for
+//   producers   one thread per pipeline: per 128-byte K block one 2-D tensor copy of the weight
+//               tile (128 rows x 128 B, 128-byte swizzle) and one of the activations (BN rows x
+//               128 B) into the pipeline's ring of shared-memory stages, completion on an mbarrier.
+//   issuers     one thread per pipeline issues tcgen05.mma (kind::i8 for W8A8, kind::f8f6f4 for
 //               FP8) from shared-memory descriptors into a TMEM accumulator (128 lanes x BN
-//               fp32/int32 columns, two buffers), tcgen05.commit hands stages back / signals
-//               the epilogue.
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (a warp owns the 32 TMEM lanes = 32 vocab
+//               fp32/int32 columns, two buffers per pipeline), tcgen05.commit hands stages back /
+//               signals the epilogue.
+//   4 warps     epilogue: tcgen05.ld the accumulator (a warp owns the 32 TMEM lanes = 32 vocab
 //               rows of its quadrant), apply the mode's scale, round to fp16 like the reference
 //               launchers, store logits if asked, feed the sampler (per-slice maxima / Gumbel
-//               winners), overlapped with the next tile's MMAs through the second TMEM buffer.
+//               winners), overlapped with the next tiles' MMAs through the second TMEM buffers.
 //
 // Replaces fp8_gemm / int8_w8a8_gemm of the reference (src/vllm_quant_kernels/_kernels.py:299-477)
-// for batches above 16.  Every mbarrier wait is bounded (async_helpers.cuh).
+// for batches above 8.  Every mbarrier wait is bounded (async_helpers.cuh).
 #include "umma_common.cuh"
 
 namespace vqk {
 namespace umma {
 
-constexpr int kThreads = 192;  // producer warp, MMA warp, four epilogue warps
+// NI independent MMA pipelines ("lanes") per CTA, each with its own TMA producer thread, issuing
+// thread, stage ring and pair of accumulators, each on its own tile (the CTA's n-th tile belongs
+// to lane n % NI).  One thread issues a tcgen05 instruction about every 54 cycles and also has a
+// barrier wait and a commit per k-block, while the tensor pipe needs only 39 cycles for a
+// 128 x N x 32-byte MMA with N <= 32 (64 for N = 128): narrow batches are issue-bound with one
+// issuer, and extra lanes hide each other's bookkeeping.
+__host__ __device__ inline int umma_threads(int ni) { return (2 * ni + 4) * 32; }
+constexpr int kPerLane = 2 * kMaxStages;  // barriers per lane: full, empty
 
 struct Geometry {
   int stage_bytes;  // A tile + B tile
-  int stages;
+  int stages_per_lane;
   size_t total;
 };
-__host__ __device__ inline Geometry geometry(int bn) {
+__host__ __device__ inline Geometry geometry(int bn, int ni) {
   Geometry g;
   g.stage_bytes = BM * BK + bn * BK;
-  const size_t fixed = 1024 /* alignment slack */ + 256 /* barriers */ + (size_t)bn * sizeof(RowMeta) +
+  const size_t fixed = 1024 /* alignment slack */ + 1024 /* barriers */ + (size_t)bn * sizeof(RowMeta) +
                        (size_t)12 * bn * sizeof(int) /* sampler state */;
   const size_t limit = 227 * 1024;
-  int s = (int)((limit - fixed) / g.stage_bytes);
-  g.stages = s > kMaxStages ? kMaxStages : s;
-  g.total = fixed + (size_t)g.stages * g.stage_bytes;
+  int s = (int)((limit - fixed) / g.stage_bytes) / ni;
+  g.stages_per_lane = s > kMaxStages ? kMaxStages : s;
+  g.total = fixed + (size_t)ni * g.stages_per_lane * g.stage_bytes;
   return g;
 }
 
-
-template <int MODE, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int MODE, int BN, int NI>
+__global__ void __launch_bounds__((2 * NI + 4) * 32, 1)
 k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB) {
   constexpr bool INT8 = (MODE == VQK_MODE_W8A8);
-  constexpr uint32_t TCOLS = (2 * BN <= 32) ? 32u : (uint32_t)(2 * BN);  // power of two for BN in {16..256}
+  constexpr int kThreadsHere = (2 * NI + 4) * 32;
+  constexpr uint32_t kNeed = (uint32_t)(NI * 2 * BN);
+  constexpr uint32_t TCOLS = kNeed <= 32 ? 32u : kNeed <= 64 ? 64u : kNeed <= 128 ? 128u : kNeed <= 256 ? 256u : 512u;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const Geometry geo = geometry(BN);
-  const int S = geo.stages;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)S * geo.stage_bytes);
-  uint64_t* full = bars;
-  uint64_t* empty = bars + kMaxStages;
-  uint64_t* tfull = bars + 2 * kMaxStages;
-  uint64_t* tempty = bars + 2 * kMaxStages + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
+  const Geometry geo = geometry(BN, NI);
+  const int S = geo.stages_per_lane;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NI * S * geo.stage_bytes);
+  uint64_t* tfull = bars;            // [NI * 2]
+  uint64_t* tempty = bars + 2 * NI;  // [NI * 2]
+  uint64_t* lane_bars = bars + 4 * NI;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(lane_bars + NI * kPerLane);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  RowMeta* meta = reinterpret_cast<RowMeta*>(bars + 32);
+  RowMeta* meta = reinterpret_cast<RowMeta*>(bars + 128);
   int* sstate = reinterpret_cast<int*>(meta + BN);  // [4 warps][3][BN] sampler state of the epilogue warps
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -66,19 +73,20 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
   const int ntiles = (V + BM - 1) / BM;
 
   if (tid == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int r = 0; r < 2; ++r) { mbar_init(&tfull[r], 1); mbar_init(&tempty[r], 4); }
+    for (int i = 0; i < 2 * NI; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int l = 0; l < NI; ++l)
+      for (int s = 0; s < S; ++s) { mbar_init(&lane_bars[l * kPerLane + s], 1); mbar_init(&lane_bars[l * kPerLane + kMaxStages + s], 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (p.do_sample)
-    for (int b = tid; b < BN; b += kThreads) {
+    for (int b = tid; b < BN; b += kThreadsHere) {
       RowMeta m;
       m.flags = 0; m.T = 1.f; m.thr = -INFINITY; m.top_p = 1.f; m.top_k = 0; m.seed = 0;
       if (b < B) m = decode_row(p.sp, b);
       meta[b] = m;
     }
-  if (warp == 1) {
+  if (warp == NI) {  // the first issuing warp owns the TMEM allocation
     tmem_alloc(tmem_slot, TCOLS);
     tmem_relinquish();
   }
@@ -86,60 +94,71 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // this CTA's n-th tile is blockIdx.x + n * gridDim.x; lane l takes n = l, l + NI, ...
+  const int mytiles = (int)blockIdx.x < ntiles ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-  if (warp == 0) {
-    // ================================ TMA producer =====================================
+  if (warp < NI) {
+    // ================================ TMA producers =====================================
     if (lane == 0) {
-      int it = 0;
+      const int l = warp;
+      uint64_t* full = lane_bars + l * kPerLane;
+      uint64_t* empty = full + kMaxStages;
+      uint8_t* my = smem + (size_t)l * S * geo.stage_bytes;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (uint32_t)(it / S) & 1u;
+      for (int n = l; n < mytiles && ok; n += NI) {
+        const int row0 = (blockIdx.x + n * gridDim.x) * BM;
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-          uint8_t* sa = smem + (size_t)s * geo.stage_bytes;
-          uint8_t* sb = sa + BM * BK;
+          uint8_t* sa = my + (size_t)s * geo.stage_bytes;
           mbar_expect_tx(&full[s], (uint32_t)geo.stage_bytes);
-          tma_load_2d(sa, &mapA, kb * BK, tile * BM, &full[s]);
-          tma_load_2d(sb, &mapB, kb * BK, 0, &full[s]);
+          tma_load_2d(sa, &mapA, kb * BK, row0, &full[s]);
+          tma_load_2d(sa + BM * BK, &mapB, kb * BK, 0, &full[s]);
+          if (++s == S) { s = 0; ph ^= 1u; }
         }
       }
     }
-  } else if (warp == 1) {
-    // ================================ MMA issuer =======================================
+  } else if (warp < 2 * NI) {
+    // ================================ MMA issuers =======================================
+    // Counters and constant increments only: everything in this loop delays the next MMA.
     if (lane == 0) {
+      const int l = warp - NI;
+      uint64_t* full = lane_bars + l * kPerLane;
+      uint64_t* empty = full + kMaxStages;
       const uint32_t idesc = instr_desc(INT8, BN);
-      int it = 0, tcount = 0;
+      const uint64_t adesc0 = smem_desc_sw128(smem_u32(smem + (size_t)l * S * geo.stage_bytes));
+      const uint64_t kStageStep = (uint64_t)geo.stage_bytes >> 4;
+      int s = 0, u = 0;
+      uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-        const int buf = tcount & 1;
-        const uint32_t tph = (uint32_t)(tcount >> 1) & 1u;
-        if (!mbar_wait(&tempty[buf], tph ^ 1u, abort_flag)) break;
+      for (int n = l; n < mytiles && ok; n += NI, ++u) {
+        const int acc = l * 2 + (u & 1);
+        if (!mbar_wait(&tempty[acc], ((uint32_t)(u >> 1) & 1u) ^ 1u, abort_flag)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (uint32_t)(it / S) & 1u;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)s * geo.stage_bytes);
-          const uint64_t adesc = smem_desc_sw128(sa);
-          const uint64_t bdesc = smem_desc_sw128(sa + BM * BK);
-#pragma unroll
-          for (int k = 0; k < BK / 32; ++k)  // +32 bytes of K = +2 in the 16-byte address field
-            umma_8bit<INT8>(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          const uint64_t adesc = adesc0 + (uint64_t)s * kStageStep;
+          const uint64_t bdesc = adesc + ((uint64_t)(BM * BK) >> 4);
+          // +32 bytes of K = +2 in the 16-byte address field
+          umma_8bit<INT8>(d_tmem, adesc, bdesc, idesc, kb != 0 ? 1u : 0u);
+          umma_8bit<INT8>(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
+          umma_8bit<INT8>(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
+          umma_8bit<INT8>(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
           umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+          if (++s == S) { s = 0; ph ^= 1u; }
         }
-        if (ok) umma_commit(&tfull[buf]);  // accumulator complete
+        if (ok) umma_commit(&tfull[acc]);  // accumulator complete
       }
     }
   } else {
-    umma_epilogue<INT8 ? 1 : 0, BN>(p, warp, lane, tmem_base, tfull, tempty, abort_flag, meta, sstate, ntiles);
+    umma_epilogue<INT8 ? 1 : 0, BN, NI>(p, warp, lane, tmem_base, tfull, tempty, abort_flag, meta, sstate, ntiles);
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == NI) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TCOLS);
   }
@@ -178,20 +197,36 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, long long 
   return r == CUDA_SUCCESS ? VQK_OK : VQK_ERR_CUDA;
 }
 
-template <int MODE, int BN>
-static int launch_one(const LmHeadParams& p, const CUtensorMap& a, const CUtensorMap& b, int grid, cudaStream_t st) {
-  const Geometry geo = geometry(BN);
+template <int MODE, int BN, int NI>
+static int launch_lanes(const LmHeadParams& p, const CUtensorMap& a, const CUtensorMap& b, int grid, cudaStream_t st) {
+  const Geometry geo = geometry(BN, NI);
+  if (geo.stages_per_lane < 2) return VQK_ERR_UNSUPPORTED;
   static bool configured[64] = {};
   int dev = 0;
   VQK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
   if (!configured[dev]) {
-    VQK_CUDA(cudaFuncSetAttribute(k_lm_head_umma<MODE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)geo.total));
+    VQK_CUDA(cudaFuncSetAttribute(k_lm_head_umma<MODE, BN, NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)geo.total));
     configured[dev] = true;
   }
-  k_lm_head_umma<MODE, BN><<<grid, kThreads, geo.total, st>>>(p, a, b);
+  // every CTA of the grid runs (those without a tile still write their empty slice records)
+  k_lm_head_umma<MODE, BN, NI><<<grid, umma_threads(NI), geo.total, st>>>(p, a, b);
   VQK_LAUNCH_CHECK();
   return VQK_OK;
+}
+// three pipelines for narrow batch tiles (issue-bound), two at 64, one from 128 columns on (the
+// MMAs are long enough, and the accumulators fill TMEM)
+template <int MODE, int BN>
+static int launch_one(const LmHeadParams& p, const CUtensorMap& a, const CUtensorMap& b, int grid, cudaStream_t st) {
+  static const int cap = [] {
+    const char* e = getenv("VQK_UMMA_LANES");  // tuning knob: fewer MMA pipelines per CTA
+    const int v = e ? atoi(e) : 0;
+    return v >= 1 && v <= 3 ? v : 3;
+  }();
+  constexpr int kWant = BN <= 32 ? 3 : BN <= 64 ? 2 : 1;
+  if (kWant >= 3 && cap >= 3) return launch_lanes<MODE, BN, 3>(p, a, b, grid, st);
+  if (kWant >= 2 && cap >= 2) return launch_lanes<MODE, BN, (BN <= 128 ? 2 : 1)>(p, a, b, grid, st);
+  return launch_lanes<MODE, BN, 1>(p, a, b, grid, st);
 }
 
 template <int MODE>

@@ -101,7 +101,10 @@ __device__ __forceinline__ float key_to_float(int k) {
 // Epilogue of the tensor-core lm_head kernels, run by the four epilogue warps (warp % 4 = TMEM
 // lane quadrant).  EPI: 0 = fp32 accumulator x fp16/fp32 row scale, 1 = int32 accumulator x row
 // scale x activation scale (W8A8), 2 = fp32 accumulator as is (MX modes).
-template <int EPI, int BN>
+// NI: independent MMA pipelines ("lanes") in the CTA.  The CTA's n-th tile is computed by lane
+// n % NI into that lane's accumulator (n / NI) % 2, at TMEM columns ((n % NI) * 2 + buffer) * BN,
+// and announced / released through tfull / tempty at the same index.
+template <int EPI, int BN, int NI = 1>
 __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, int lane, uint32_t tmem_base,
                                               uint64_t* tfull, uint64_t* tempty, volatile int* abort_flag,
                                               const RowMeta* meta, int* sstate, int ntiles) {
@@ -122,8 +125,8 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
 
     int tcount = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
-      const int buf = tcount & 1;
-      const uint32_t tph = (uint32_t)(tcount >> 1) & 1u;
+      const int buf = (tcount % NI) * 2 + ((tcount / NI) & 1);
+      const uint32_t tph = (uint32_t)((tcount / NI) >> 1) & 1u;
       const int row = tile * BM + q * 32 + lane;
       const bool rok = row < V;
       const int rowc = rok ? row : V - 1;  // clamped: out-of-range lanes write nothing
