@@ -214,6 +214,29 @@ int vqk_comm_create(const void* id_host, int rank, int nranks, vqk_comm** out);
 int vqk_comm_allgather(vqk_comm* c, const void* send, void* recv, int64_t bytes_per_rank, void* stream);
 int vqk_comm_destroy(vqk_comm* c);
 
+/* ---------------------------------------------------------------------------
+ * The same exchange without NCCL, fused with the merge (no counterpart in the
+ * reference): every rank (one process per GPU, all on one node) owns a landing
+ * buffer that its peers map through CUDA IPC; ONE kernel copies this rank's records
+ * into every rank's buffer with plain peer stores over NVLink, publishes a per-row
+ * step number, waits (bounded: a peer that never arrives gives token -1 and sets
+ * vqk_device_error) for the other ranks' records of the same step and merges them.
+ * All ranks must make the same sequence of calls with the same B.  Safe to capture
+ * in a CUDA graph (the step number lives in device memory).
+ *   vqk_peer_create   allocates the landing buffer (not on the hot path) and returns
+ *                     the handle to hand to every other rank (any transport).
+ *   vqk_peer_connect  takes all ranks' handles, rank-major, own one included.
+ * ------------------------------------------------------------------------- */
+typedef struct vqk_peer vqk_peer;
+#define VQK_PEER_HANDLE_BYTES 64
+#define VQK_PEER_MAX_RANKS 8
+int vqk_peer_create(int rank, int nranks, int64_t max_rows, vqk_peer** out,
+                    void* handle_out_host /* VQK_PEER_HANDLE_BYTES */);
+int vqk_peer_connect(vqk_peer* p, const void* all_handles_host /* nranks * VQK_PEER_HANDLE_BYTES */);
+int vqk_peer_exchange_finalize(vqk_peer* p, const void* records /* [B, VQK_RECORD_BYTES] device */, int64_t B,
+                               const vqk_sample_params* sp, int64_t* tokens, float* scores, void* stream);
+int vqk_peer_destroy(vqk_peer* p);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,8 +1,10 @@
 """Worker of tests/test_gpu_multi.py (launched by torch.distributed.run, one rank per GPU).
 
 Every rank builds the same seeded weights, keeps its vocab slice, and runs the sharded step
-twice: once exchanging records through libvqk's own NCCL communicator, once through
-torch.distributed.  Rank 0 also runs the unsharded step; all results must be identical."""
+three times: exchanging records through libvqk's own NCCL communicator, through
+torch.distributed, and through the fused peer-memory exchange (also replayed from a CUDA graph
+several times, which exercises the step counters and the two landing-buffer parities).  Every
+rank also runs the unsharded step; all results must be identical."""
 
 import os
 import sys
@@ -18,7 +20,8 @@ import torch.distributed as dist  # noqa: E402
 
 def main():
     from vllm_quant_kernels import _lmhead as LH
-    from vllm_quant_kernels._dist import VocabShardedLMHead, VqkComm, shard_bounds
+    from vllm_quant_kernels import _ffi
+    from vllm_quant_kernels._dist import VocabShardedLMHead, VqkComm, VqkPeer, shard_bounds
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -39,6 +42,7 @@ def main():
                                t(kw.get("top_p"), torch.float32), None, 0, V)
 
     comm = VqkComm(rank, world)
+    peer = VqkPeer(rank, world, max_rows=16)
     a, b = shard_bounds(V, world, rank)
     for mode in ("int8", "mxfp4"):
         q, s = LH.quantize_weight(mode, w)
@@ -52,7 +56,30 @@ def main():
                 torch.cuda.synchronize()
                 assert torch.equal(tok, ref_tok), (rank, mode, list(kw), tok.tolist(), ref_tok.tolist())
                 assert torch.equal(sc, ref_sc)
+            ph = VocabShardedLMHead(mine, a, V, peer=peer)
+            for _ in range(3):  # both parities of the landing buffer
+                tok, sc = ph.step(x, sp)
+                torch.cuda.synchronize()
+                assert torch.equal(tok, ref_tok), ("peer", rank, mode, list(kw), tok.tolist(), ref_tok.tolist())
+                assert torch.equal(sc, ref_sc)
+    # the peer step inside a CUDA graph: the step number lives on the device, so replays stay in step
+    sp = args()
+    ph = VocabShardedLMHead(mine, a, V, peer=peer)
+    ref_tok, _ = full.sample(x, sp)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ph.step(x, sp)  # warm-up outside the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            gtok, _ = ph.step(x, sp)
+        for _ in range(5):
+            graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(gtok, ref_tok), ("peer graph", rank, gtok.tolist(), ref_tok.tolist())
+    assert _ffi.lib().vqk_device_error() == 0
     dist.barrier()
+    peer.close()
     comm.close()
     if rank == 0:
         print("MULTI_GPU_OK", flush=True)

@@ -122,8 +122,8 @@ extern "C" const char* vqk_strerror(int s) {
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int vqk_device_error(void) {
-  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag();
-  return (a < 0 || b < 0 || c < 0) ? -1 : (a | b | c);
+  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag(), d = peer_error_flag();
+  return (a < 0 || b < 0 || c < 0 || d < 0) ? -1 : (a | b | c | d);
 }
 
 extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
@@ -430,5 +430,89 @@ extern "C" int vqk_comm_destroy(vqk_comm* c) {
   NcclApi* a = nccl();
   if (a) a->CommDestroy(c->comm);
   delete c;
+  return VQK_OK;
+}
+
+// ---- record exchange over peer memory ---------------------------------------------------------------
+struct vqk_peer {
+  int rank, nranks;
+  long long max_rows;
+  void* local;       // own landing buffer | flag words | step counters
+  void* mapped[8];   // peers' buffers opened through CUDA IPC (null for the own rank)
+  PeerTable pt;
+  bool connected;
+};
+namespace {
+size_t peer_data_bytes(int G, long long rows) { return (size_t)2 * G * rows * VQK_RECORD_BYTES; }
+size_t peer_flag_bytes(int G, long long rows) { return (((size_t)G * rows * sizeof(unsigned int)) + 255) & ~(size_t)255; }
+}  // namespace
+
+extern "C" int vqk_peer_create(int rank, int nranks, int64_t max_rows, vqk_peer** out, void* handle_out_host) {
+  if (!out || !handle_out_host || nranks <= 0 || nranks > VQK_PEER_MAX_RANKS || rank < 0 || rank >= nranks ||
+      max_rows <= 0 || max_rows > 65535)
+    return VQK_ERR_INVALID;
+  static_assert(sizeof(cudaIpcMemHandle_t) == VQK_PEER_HANDLE_BYTES, "IPC handle size");
+  *out = nullptr;
+  int rc = require_sm100();
+  if (rc) return rc;
+  const size_t bytes = peer_data_bytes(nranks, max_rows) + peer_flag_bytes(nranks, max_rows) + (size_t)max_rows * sizeof(unsigned int);
+  void* base = nullptr;
+  VQK_CUDA(cudaMalloc(&base, bytes));
+  cudaError_t e = cudaMemset(base, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, base);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = (int)e;
+    cudaFree(base);
+    return VQK_ERR_CUDA;
+  }
+  vqk_peer* p = new (std::nothrow) vqk_peer();
+  if (!p) { cudaFree(base); return VQK_ERR_INVALID; }
+  p->rank = rank; p->nranks = nranks; p->max_rows = max_rows; p->local = base; p->connected = false;
+  memcpy(handle_out_host, &h, sizeof(h));
+  *out = p;
+  return VQK_OK;
+}
+
+extern "C" int vqk_peer_connect(vqk_peer* p, const void* all_handles_host) {
+  if (!p || !all_handles_host || p->connected) return VQK_ERR_INVALID;
+  const size_t data = peer_data_bytes(p->nranks, p->max_rows), flags = peer_flag_bytes(p->nranks, p->max_rows);
+  for (int g = 0; g < p->nranks; ++g) {
+    void* base = p->local;
+    if (g != p->rank) {
+      cudaIpcMemHandle_t h;
+      memcpy(&h, (const uint8_t*)all_handles_host + (size_t)g * VQK_PEER_HANDLE_BYTES, sizeof(h));
+      cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        for (int q = 0; q < g; ++q)
+          if (p->mapped[q]) { cudaIpcCloseMemHandle(p->mapped[q]); p->mapped[q] = nullptr; }
+        return VQK_ERR_COMM;
+      }
+      p->mapped[g] = base;
+    }
+    p->pt.land[g] = (uint8_t*)base;
+    p->pt.flags[g] = (unsigned int*)((uint8_t*)base + data);
+  }
+  p->pt.steps = (unsigned int*)((uint8_t*)p->local + data + flags);
+  p->connected = true;
+  return VQK_OK;
+}
+
+extern "C" int vqk_peer_exchange_finalize(vqk_peer* p, const void* records, int64_t B, const vqk_sample_params* sp,
+                                          int64_t* tokens, float* scores, void* stream) {
+  if (!p || !p->connected || !records || !sp || !tokens || B < 0) return VQK_ERR_INVALID;
+  if (B > p->max_rows) return VQK_ERR_TOO_LARGE;
+  return launch_peer_exchange((const uint8_t*)records, (int)B, p->rank, p->nranks, (int)p->max_rows, p->pt, to_dev(sp),
+                              (long long*)tokens, scores, (cudaStream_t)stream);
+}
+
+extern "C" int vqk_peer_destroy(vqk_peer* p) {
+  if (!p) return VQK_OK;
+  for (int g = 0; g < p->nranks; ++g)
+    if (p->mapped[g]) cudaIpcCloseMemHandle(p->mapped[g]);
+  if (p->local) cudaFree(p->local);
+  delete p;
   return VQK_OK;
 }

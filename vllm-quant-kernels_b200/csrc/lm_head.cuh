@@ -77,6 +77,15 @@ int launch_select(const SelectParams& p, cudaStream_t st);
 // merge gathered records
 int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, long long* tokens, float* scores,
                     cudaStream_t st);
+// record exchange over peer memory fused with the merge (sampler.cu: k_peer_exchange)
+struct PeerTable {
+  uint8_t* land[8];        // every rank's landing buffer [2][G][max_rows][VQK_RECORD_BYTES] (own one included)
+  unsigned int* flags[8];  // every rank's flag words [G][max_rows]
+  unsigned int* steps;     // this rank's step counters [max_rows]
+};
+int launch_peer_exchange(const uint8_t* mine, int B, int rank, int G, int max_rows, const PeerTable& pt,
+                         const SampleDev& sp, long long* tokens, float* scores, cudaStream_t st);
+int peer_error_flag();
 // sampler on materialised logits with its scratch in a static device array (no allocation)
 int sample_static(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, long long* tokens,
                   float* scores, cudaStream_t st);

@@ -517,9 +517,10 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kSelThrea
 }
 
 // ---- merge of gathered shard records -----------------------------------------------------------
-__global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ records, int G, int B, SampleDev sp,
-                                                  long long* tokens, float* scores) {
-  const int b = blockIdx.x, tid = threadIdx.x;
+// record of rank g for row b: records + g * rank_stride + b * VQK_RECORD_BYTES
+__device__ __forceinline__ void finalize_row(const uint8_t* __restrict__ records, size_t rank_stride, int G, int b,
+                                             const SampleDev& sp, long long* tokens, float* scores) {
+  const int tid = threadIdx.x;
   const RowMeta m = decode_row(sp, b);
   __shared__ float s_cv[kGlobalCap];
   __shared__ int s_ct[kGlobalCap];
@@ -533,7 +534,7 @@ __global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ re
   if (tid == 0) {
     int n = 0, bad = 0;
     for (int g = 0; g < G; ++g) {
-      const RecordHeader* h = reinterpret_cast<const RecordHeader*>(records + ((size_t)g * B + b) * VQK_RECORD_BYTES);
+      const RecordHeader* h = reinterpret_cast<const RecordHeader*>(records + g * rank_stride + (size_t)b * VQK_RECORD_BYTES);
       if (h->flags) bad = 1;
       n += h->n;
     }
@@ -549,7 +550,7 @@ __global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ re
     if (tid == 0) {
       Best best{-INFINITY, 0x7fffffff};
       for (int g = 0; g < G; ++g) {
-        const RecordHeader* h = reinterpret_cast<const RecordHeader*>(records + ((size_t)g * B + b) * VQK_RECORD_BYTES);
+        const RecordHeader* h = reinterpret_cast<const RecordHeader*>(records + g * rank_stride + (size_t)b * VQK_RECORD_BYTES);
         if (better(h->score, h->token, best.s, best.t)) { best.s = h->score; best.t = h->token; }
       }
       tokens[b] = best.t;
@@ -559,7 +560,7 @@ __global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ re
   }
   int base = 0;
   for (int g = 0; g < G; ++g) {
-    const uint8_t* rec = records + ((size_t)g * B + b) * VQK_RECORD_BYTES;
+    const uint8_t* rec = records + g * rank_stride + (size_t)b * VQK_RECORD_BYTES;
     const int c = reinterpret_cast<const RecordHeader*>(rec)->n;
     const Cand* cd = reinterpret_cast<const Cand*>(rec + sizeof(RecordHeader));
     for (int i = tid; i < c; i += blockDim.x) { s_cv[base + i] = cd[i].v; s_ct[base + i] = cd[i].t; }
@@ -568,6 +569,68 @@ __global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ re
   __syncthreads();
   Best w = resolve_candidates(s_cv, s_ct, s_n, m, s_y, s_w, s_alive, s_redb, s_redf, &s_z);
   if (tid == 0) { tokens[b] = w.t; if (scores) scores[b] = w.s; }
+}
+
+__global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ records, int G, int B, SampleDev sp,
+                                                  long long* tokens, float* scores) {
+  finalize_row(records, (size_t)B * VQK_RECORD_BYTES, G, blockIdx.x, sp, tokens, scores);
+}
+
+// ---- record exchange over peer memory + merge, one kernel ------------------------------------------
+// Every rank owns a landing buffer [2 parities][G ranks][max_rows] records, a flag word per
+// (rank, row) and a step counter per row.  The CTA of row b copies its rank's record into slot
+// [parity][rank][b] of EVERY rank's landing buffer (plain stores through NVLink peer mappings),
+// fences, publishes the row's step number in the matching flag word of every rank, then waits
+// (bounded) until the G flag words of its own buffer carry this step and merges the G records.
+// The step number lives in device memory, so a CUDA-graph replay advances it like a fresh
+// launch.  Two parities are enough: a rank can enter step t + 2 only after it has seen every
+// peer's flag of step t + 1, which a peer raises after it has finished reading step t.
+static __device__ int g_peer_error = 0;
+constexpr unsigned int kPeerSpinLimit = 1u << 22;  // x ~50 ns: about 0.2 s, then the row reports -1
+
+__global__ void __launch_bounds__(256) k_peer_exchange(const uint8_t* __restrict__ mine, int B, int rank, int G,
+                                                       int max_rows, PeerTable pt, SampleDev sp, long long* tokens,
+                                                       float* scores) {
+  const int b = blockIdx.x, tid = threadIdx.x;
+  __shared__ unsigned int s_step;
+  __shared__ int s_late;
+  if (tid == 0) {
+    unsigned int* steps = pt.steps;
+    s_step = steps[b] + 1u;
+    steps[b] = s_step;
+    s_late = 0;
+  }
+  __syncthreads();
+  const unsigned int step = s_step;
+  const size_t slot = (((size_t)(step & 1u) * G + rank) * max_rows + b) * VQK_RECORD_BYTES;
+  const uint4* src = reinterpret_cast<const uint4*>(mine + (size_t)b * VQK_RECORD_BYTES);
+  for (int i = tid; i < G * (VQK_RECORD_BYTES / 16); i += blockDim.x) {
+    const int g = i / (VQK_RECORD_BYTES / 16), c = i % (VQK_RECORD_BYTES / 16);
+    reinterpret_cast<uint4*>(pt.land[g] + slot)[c] = src[c];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < G) {
+    unsigned int* f = pt.flags[tid] + (size_t)rank * max_rows + b;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
+    // wait for rank `tid`'s record of this step in the local buffer
+    const unsigned int* w = pt.flags[rank] + (size_t)tid * max_rows + b;
+    bool ok = false;
+    for (unsigned int it = 0; it < kPeerSpinLimit; ++it) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
+      if ((int)(v - step) >= 0) { ok = true; break; }
+      __nanosleep(40);
+    }
+    if (!ok) { s_late = 1; atomicExch(&g_peer_error, 1); }
+  }
+  __syncthreads();
+  if (s_late) {
+    if (tid == 0) { tokens[b] = -1; if (scores) scores[b] = -INFINITY; }
+    return;
+  }
+  const uint8_t* landed = pt.land[rank] + (size_t)(step & 1u) * G * max_rows * VQK_RECORD_BYTES;
+  finalize_row(landed, (size_t)max_rows * VQK_RECORD_BYTES, G, b, sp, tokens, scores);
 }
 
 template <typename T>
@@ -618,6 +681,19 @@ int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, l
   k_finalize<<<(unsigned)B, 256, 0, st>>>(records, G, B, sp, tokens, scores);
   VQK_LAUNCH_CHECK();
   return VQK_OK;
+}
+
+int launch_peer_exchange(const uint8_t* mine, int B, int rank, int G, int max_rows, const PeerTable& pt,
+                         const SampleDev& sp, long long* tokens, float* scores, cudaStream_t st) {
+  if (B == 0) return VQK_OK;
+  k_peer_exchange<<<(unsigned)B, 256, 0, st>>>(mine, B, rank, G, max_rows, pt, sp, tokens, scores);
+  VQK_LAUNCH_CHECK();
+  return VQK_OK;
+}
+int peer_error_flag() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
 }
 
 int launch_topk_threshold(const void* logits, int dtype, long long ld, int B, int V, const int32_t* top_k, float* thr,

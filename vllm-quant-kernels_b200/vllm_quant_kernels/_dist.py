@@ -3,8 +3,10 @@
 Rows of the lm_head weight are independent, so rank r owns a contiguous vocab
 slice and computes its slice of the logits plus a small per-row *record*: its
 Gumbel winner, or its top-k candidates when top-k / top-p is active.  One tiny
-all-gather of the records (1 KiB per row per rank) is the only exchange; every
-rank then resolves the same final token.  Philox noise is indexed by the GLOBAL
+exchange of the records (1 KiB per row per rank) is the only communication: an
+all-gather (NCCL) followed by a merge kernel, or, with `VqkPeer`, one kernel that
+stores the records into every rank's buffer over NVLink peer mappings, waits for
+the peers' records and merges.  Every rank resolves the same final token.  Philox noise is indexed by the GLOBAL
 token id, so the answer does not depend on the number of shards.
 
 The reference plugin is single-GPU; the merge has the shape of vLLM's
@@ -68,6 +70,51 @@ class VqkComm:
             self._h = None
 
 
+class VqkPeer:
+    """Record exchange over peer memory (CUDA IPC mappings, one process per GPU on one
+    node), fused with the merge into ONE kernel: no NCCL call on the step.  The IPC
+    handles travel through torch.distributed once, at construction."""
+
+    def __init__(self, rank: int, world: int, max_rows: int = 256, group=None, device=None):
+        import torch.distributed as dist
+        if world > _ffi.PEER_MAX_RANKS:
+            raise ValueError(f"at most {_ffi.PEER_MAX_RANKS} ranks")
+        L = _ffi.lib()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        h = ctypes.c_void_p()
+        mine = ctypes.create_string_buffer(_ffi.PEER_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            _ffi.check(L.vqk_peer_create(rank, world, max_rows, ctypes.byref(h), mine))
+        self._h = h
+        handles = [None] * world
+        dist.all_gather_object(handles, mine.raw, group=group)
+        with torch.cuda.device(self.device):
+            _ffi.check(L.vqk_peer_connect(self._h, b"".join(handles)))
+        dist.barrier(group=group)  # nobody pushes before every rank has mapped every buffer
+        self.rank, self.world, self.max_rows = rank, world, max_rows
+
+    def exchange_finalize(self, rec: torch.Tensor, sp: SamplingArgs):
+        """This rank's records [B, 1024] in, (tokens, scores) of the merged step out;
+        identical on every rank.  A peer that never shows up gives token -1."""
+        assert rec.is_cuda and rec.dtype == torch.uint8 and rec.dim() == 2 and rec.shape[1] == _ffi.RECORD_BYTES
+        rec = rec.contiguous()
+        B = rec.shape[0]
+        tokens = torch.empty(B, dtype=torch.int64, device=rec.device)
+        scores = torch.empty(B, dtype=torch.float32, device=rec.device)
+        spc = sp.to_c(B, sp.vocab_total if sp.vocab_total is not None else 0)
+        if B:
+            with torch.cuda.device(rec.device):
+                _ffi.check(_ffi.lib().vqk_peer_exchange_finalize(
+                    self._h, rec.data_ptr(), B, ctypes.byref(spc), tokens.data_ptr(), scores.data_ptr(),
+                    torch.cuda.current_stream(rec.device).cuda_stream))
+        return tokens, scores
+
+    def close(self):
+        if self._h:
+            _ffi.lib().vqk_peer_destroy(self._h)
+            self._h = None
+
+
 def exchange_records(rec: torch.Tensor, group=None, comm: Optional[VqkComm] = None) -> torch.Tensor:
     """All-gather per-rank records [B, 1024] into [G, B, 1024] (rank-major).  With a
     VqkComm the collective runs on the current CUDA stream; otherwise through
@@ -89,12 +136,13 @@ class VocabShardedLMHead:
     """One rank's part of a vocab-sharded lm_head + sampler step."""
 
     def __init__(self, shard: LMHeadShard, vocab_start: int, vocab_total: int, group=None,
-                 comm: Optional[VqkComm] = None):
+                 comm: Optional[VqkComm] = None, peer: Optional["VqkPeer"] = None):
         self.shard = shard
         self.vocab_start = int(vocab_start)
         self.vocab_total = int(vocab_total)
         self.group = group
         self.comm = comm
+        self.peer = peer  # exchange over peer memory fused with the merge; else all-gather + finalize
 
     def local_args(self, sp: SamplingArgs) -> SamplingArgs:
         return SamplingArgs(sp.temperature, sp.seeds, sp.top_k, sp.top_p, sp.topk_threshold,
@@ -104,6 +152,8 @@ class VocabShardedLMHead:
         """(tokens int64 [B], scores fp32 [B]), identical on every rank."""
         lsp = self.local_args(sp)
         rec = self.shard.shard_records(hidden_states, lsp, bias)
+        if self.peer is not None:
+            return self.peer.exchange_finalize(rec, lsp)
         gathered = exchange_records(rec, self.group, self.comm)
         return finalize_records(gathered, lsp)
 

@@ -18,6 +18,8 @@ F16, BF16, F32 = range(3)
 RECORD_BYTES = 1024
 RECORD_CAP = 126
 COMM_ID_BYTES = 128
+PEER_HANDLE_BYTES = 64
+PEER_MAX_RANKS = 8
 STATIC_MAX_ROWS = 64
 STATIC_MAX_VOCAB = 262144
 
@@ -28,6 +30,7 @@ SYMBOLS = (
     "vqk_lm_head_set_kernel_events",
     "vqk_sample_workspace_bytes", "vqk_sample", "vqk_sample_static", "vqk_sample_finalize", "vqk_topk_threshold",
     "vqk_comm_unique_id", "vqk_comm_create", "vqk_comm_allgather", "vqk_comm_destroy",
+    "vqk_peer_create", "vqk_peer_connect", "vqk_peer_exchange_finalize", "vqk_peer_destroy",
 )
 
 
@@ -84,6 +87,11 @@ def lib() -> ctypes.CDLL:
     L.vqk_comm_create.argtypes = [c_void_p, c_int, c_int, POINTER(c_void_p)]
     L.vqk_comm_allgather.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     L.vqk_comm_destroy.argtypes = [c_void_p]
+    L.vqk_peer_create.argtypes = [c_int, c_int, c_int64, POINTER(c_void_p), c_void_p]
+    L.vqk_peer_connect.argtypes = [c_void_p, c_void_p]
+    L.vqk_peer_exchange_finalize.argtypes = [c_void_p, c_void_p, c_int64, POINTER(SampleParams), c_void_p, c_void_p,
+                                             c_void_p]
+    L.vqk_peer_destroy.argtypes = [c_void_p]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if fn.restype is c_int and name not in ("vqk_version", "vqk_last_cuda_error", "vqk_device_error"):
