@@ -78,69 +78,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   const int ngroups = K / GROUP;
   const int nks = (K + 63) / 64;
 
-  // ---- prologue: activations -> B fragments in shared memory -------------------------
-  if constexpr (MODE == VQK_MODE_W8A16) {
-    const int total = nks * 4 * NT * 32;
-    for (int s = tid; s < total; s += kThreads) {
-      int l = s & 31, nt = (s >> 5) % NT, i = (s / (32 * NT)) & 3, ks = s / (128 * NT);
-      int b = nt * 8 + (l >> 2), k = ks * 64 + (l & 3) * 16 + i * 4;
-      __half h[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        // fragment order 0, 2, 1, 3: the weight expansion pairs bytes (0,2) and (1,3) of a word
-        const int kk = k + ((j & 1) * 2) + (j >> 1);
-        float v = 0.f;
-        if (b < B && kk < K) {
-          v = p.x_dtype == VQK_BF16
-                  ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.x)[(long long)b * p.ldx + kk])
-                  : __half2float(reinterpret_cast<const __half*>(p.x)[(long long)b * p.ldx + kk]);
-        }
-        h[j] = __float2half_rn(v);
-      }
-      xfrag[s] = *reinterpret_cast<uint2*>(h);
-    }
-  } else if constexpr (!MX) {
-    const int total = nks * 2 * NT * 32;
-    const uint8_t* xq = reinterpret_cast<const uint8_t*>(p.x);
-    for (int s = tid; s < total; s += kThreads) {
-      int l = s & 31, nt = (s >> 5) % NT, i = (s / (32 * NT)) & 1, ks = s / (64 * NT);
-      int b = nt * 8 + (l >> 2), k = ks * 64 + (l & 3) * 16 + i * 8;
-      uint2 v = make_uint2(0, 0);
-      if (b < B && k < K) v = *reinterpret_cast<const uint2*>(xq + (long long)b * K + k);
-      xfrag[s] = v;
-    }
-  } else {
-    const int total = ngroups * NT * 32;
-    const uint8_t* xq = reinterpret_cast<const uint8_t*>(p.x);
-    const uint8_t* xs = reinterpret_cast<const uint8_t*>(p.xscale);
-    for (int s = tid; s < total; s += kThreads) {
-      int l = s & 31, nt = (s >> 5) % NT, G = s / (32 * NT);
-      int b = nt * 8 + (l >> 2), k = G * 32 + (l & 3) * 8;
-      uint2 v = make_uint2(0, 0);
-      if (b < B) {
-        v = *reinterpret_cast<const uint2*>(xq + (long long)b * K + k);
-        if constexpr (MODE == VQK_MODE_MXFP4)  // bytes 0..7 -> (0,2,4,6), (1,3,5,7) like the E2M1 expansion
-          v = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
-      }
-      xfrag[s] = v;
-    }
-    const float rescale = (MODE == VQK_MODE_MXFP4) ? kE2M1Rescale : 1.0f;
-    for (int s = tid; s < ngroups * NT * 8; s += kThreads) {
-      int c = s & 7, nt = (s >> 3) % NT, G = s / (8 * NT);
-      int b = nt * 8 + c;
-      sxf[s] = b < B ? e8m0_to_f32(xs[(long long)b * ngroups + G]) * rescale : 0.f;
-    }
-  }
-  if (p.do_sample && tid < NT * 8) {
-    RowMeta m;
-    m.flags = 0; m.T = 1.f; m.thr = -INFINITY; m.top_p = 1.f; m.top_k = 0; m.seed = 0;
-    if (tid < B) m = decode_row(p.sp, tid);
-    meta[tid] = m;
-  }
-  float xs_w8a8 = 1.f;
-  if constexpr (MODE == VQK_MODE_W8A8) xs_w8a8 = *reinterpret_cast<const float*>(p.xscale);
-  __syncthreads();
-
   // ---- per-thread sampler state: epilogue thread e of a group owns (row e%16, col e/16) ----
   const int e = tid & 127;
   const int er = e & 15, ec = e >> 4;
@@ -303,6 +240,85 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   int tile = blockIdx.x * kGroups + group, bi = 0, step = 0;
   bool have = tile < ntiles;
   if (have) issue(buf0, tile, 0);
+
+  // ---- activations -> B fragments in shared memory, while the first weight loads are in flight ----
+  if constexpr (MODE == VQK_MODE_W8A16) {
+    // one item = the four fragments (i = 0..3) a lane needs for a 64-wide k-step: the sixteen
+    // consecutive activations k .. k + 15 of batch row b, fetched with two 16-byte loads when the
+    // row allows it
+    const int items = nks * NT * 32;
+    const bool vec = p.x_dtype != VQK_BF16 && (K & 63) == 0 && ((p.ldx * 2) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+    for (int s = tid; s < items; s += kThreads) {
+      const int l = s & 31, nt = (s >> 5) % NT, ks = s / (32 * NT);
+      const int b = nt * 8 + (l >> 2), k = ks * 64 + (l & 3) * 16;
+      __align__(16) __half hv[16];
+      if (b < B && vec) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + (long long)b * p.ldx + k);
+        *reinterpret_cast<uint4*>(hv) = src[0];
+        *reinterpret_cast<uint4*>(hv + 8) = src[1];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float v = 0.f;
+          if (b < B && k + j < K) {
+            v = p.x_dtype == VQK_BF16
+                    ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.x)[(long long)b * p.ldx + k + j])
+                    : __half2float(reinterpret_cast<const __half*>(p.x)[(long long)b * p.ldx + k + j]);
+          }
+          hv[j] = __float2half_rn(v);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        // fragment order 0, 2, 1, 3: the weight expansion pairs bytes (0,2) and (1,3) of a word
+        __align__(8) __half h[4] = {hv[4 * i], hv[4 * i + 2], hv[4 * i + 1], hv[4 * i + 3]};
+        xfrag[((ks * 4 + i) * NT + nt) * 32 + l] = *reinterpret_cast<uint2*>(h);
+      }
+    }
+  } else if constexpr (!MX) {
+    const int total = nks * 2 * NT * 32;
+    const uint8_t* xq = reinterpret_cast<const uint8_t*>(p.x);
+    for (int s = tid; s < total; s += kThreads) {
+      int l = s & 31, nt = (s >> 5) % NT, i = (s / (32 * NT)) & 1, ks = s / (64 * NT);
+      int b = nt * 8 + (l >> 2), k = ks * 64 + (l & 3) * 16 + i * 8;
+      uint2 v = make_uint2(0, 0);
+      if (b < B && k < K) v = *reinterpret_cast<const uint2*>(xq + (long long)b * K + k);
+      xfrag[s] = v;
+    }
+  } else {
+    const int total = ngroups * NT * 32;
+    const uint8_t* xq = reinterpret_cast<const uint8_t*>(p.x);
+    const uint8_t* xs = reinterpret_cast<const uint8_t*>(p.xscale);
+    for (int s = tid; s < total; s += kThreads) {
+      int l = s & 31, nt = (s >> 5) % NT, G = s / (32 * NT);
+      int b = nt * 8 + (l >> 2), k = G * 32 + (l & 3) * 8;
+      uint2 v = make_uint2(0, 0);
+      if (b < B) {
+        v = *reinterpret_cast<const uint2*>(xq + (long long)b * K + k);
+        if constexpr (MODE == VQK_MODE_MXFP4)  // bytes 0..7 -> (0,2,4,6), (1,3,5,7) like the E2M1 expansion
+          v = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
+      }
+      xfrag[s] = v;
+    }
+    const float rescale = (MODE == VQK_MODE_MXFP4) ? kE2M1Rescale : 1.0f;
+    for (int s = tid; s < ngroups * NT * 8; s += kThreads) {
+      int c = s & 7, nt = (s >> 3) % NT, G = s / (8 * NT);
+      int b = nt * 8 + c;
+      sxf[s] = b < B ? e8m0_to_f32(xs[(long long)b * ngroups + G]) * rescale : 0.f;
+    }
+  }
+  if (p.do_sample && tid < NT * 8) {
+    RowMeta m;
+    m.flags = 0; m.T = 1.f; m.thr = -INFINITY; m.top_p = 1.f; m.top_k = 0; m.seed = 0;
+    if (tid < B) m = decode_row(p.sp, tid);
+    meta[tid] = m;
+  }
+  float xs_w8a8 = 1.f;
+  if constexpr (MODE == VQK_MODE_W8A8) xs_w8a8 = *reinterpret_cast<const float*>(p.xscale);
+  __syncthreads();
+
+
   while (have) {
     int ntile = tile, nbi = bi + 1;
     if (nbi == nb) { nbi = 0; ntile = tile + tstride; }

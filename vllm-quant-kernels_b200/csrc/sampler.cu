@@ -357,9 +357,10 @@ constexpr int kSelThreads = 1024;
 constexpr int kSelPreload = 4;  // 16-byte vectors per thread fetched before tau is known
 
 template <typename T>
-__global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
+__global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (int)cluster.block_rank();
+  const int csize = (int)cluster.num_blocks();  // 1, 2, 4 or 8: chosen by the launcher from the row length
   const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const RowMeta m = decode_row(p.sp, b);
   const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
@@ -416,7 +417,7 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kSelThrea
 
   // ---- put this CTA's share of the row in flight -------------------------------------------
   constexpr int VEC = 16 / (int)sizeof(T);
-  const int per = ((p.V + kClusterSize - 1) / kClusterSize + VEC - 1) / VEC * VEC;
+  const int per = ((p.V + csize - 1) / csize + VEC - 1) / VEC * VEC;
   const int c0 = min(p.V, crank * per), c1 = min(p.V, c0 + per);
   const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
   const int nvec = vec_ok ? (c1 - c0) / VEC : 0;
@@ -669,9 +670,28 @@ int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V,
 
 int launch_select(const SelectParams& p, cudaStream_t st) {
   if (p.B == 0) return VQK_OK;
-  dim3 grid(kClusterSize, (unsigned)p.B);
-  VQK_DISPATCH_DTYPE(p.dtype, (k_select<T><<<grid, kSelThreads, 0, st>>>(p)));
-  VQK_LAUNCH_CHECK();
+  // CTAs per row: enough that a CTA's share fits the registers it preloads (1024 threads x
+  // kSelPreload x 16 bytes), at most kClusterSize; short rows (a vocab shard) take one CTA and
+  // skip the cluster traffic altogether
+  const size_t esz = p.dtype == VQK_F32 ? 4 : 2;
+  const size_t share = (size_t)kSelThreads * kSelPreload * 16;
+  int cs = 1;
+  while (cs < kClusterSize && (size_t)p.V * esz > share * cs) cs <<= 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)cs, (unsigned)p.B);
+  cfg.blockDim = dim3(kSelThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaSuccess;
+  VQK_DISPATCH_DTYPE(p.dtype, (le = cudaLaunchKernelEx(&cfg, k_select<T>, p)));
+  VQK_CUDA(le);
   return VQK_OK;
 }
 
