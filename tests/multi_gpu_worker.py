@@ -60,7 +60,8 @@ def main():
             for _ in range(3):  # both parities of the landing buffer
                 tok, sc = ph.step(x, sp)
                 torch.cuda.synchronize()
-                assert torch.equal(tok, ref_tok), ("peer", rank, mode, list(kw), tok.tolist(), ref_tok.tolist())
+                assert torch.equal(tok, ref_tok), ("peer", rank, mode, list(kw), tok.tolist(), ref_tok.tolist(),
+                                                   "device_error", _ffi.lib().vqk_device_error())
                 assert torch.equal(sc, ref_sc)
     # the peer step inside a CUDA graph: the step number lives on the device, so replays stay in step
     sp = args()

@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
 
 // ---- merge of gathered shard records -----------------------------------------------------------
 // record of rank g for row b: records + g * rank_stride + b * VQK_RECORD_BYTES
-__device__ __forceinline__ void finalize_row(const uint8_t* __restrict__ records, size_t rank_stride, int G, int b,
+__device__ __forceinline__ void finalize_row(const uint8_t* records, size_t rank_stride, int G, int b,
                                              const SampleDev& sp, long long* tokens, float* scores) {
   const int tid = threadIdx.x;
   const RowMeta m = decode_row(sp, b);
@@ -587,7 +587,7 @@ __global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ re
 // launch.  Two parities are enough: a rank can enter step t + 2 only after it has seen every
 // peer's flag of step t + 1, which a peer raises after it has finished reading step t.
 static __device__ int g_peer_error = 0;
-constexpr unsigned int kPeerSpinLimit = 1u << 22;  // x ~50 ns: about 0.2 s, then the row reports -1
+constexpr unsigned int kPeerSpinLimit = 1u << 23;  // a few seconds of polling, then the row reports -1
 
 __global__ void __launch_bounds__(256) k_peer_exchange(const uint8_t* __restrict__ mine, int B, int rank, int G,
                                                        int max_rows, PeerTable pt, SampleDev sp, long long* tokens,
@@ -621,7 +621,7 @@ __global__ void __launch_bounds__(256) k_peer_exchange(const uint8_t* __restrict
       unsigned int v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
       if ((int)(v - step) >= 0) { ok = true; break; }
-      __nanosleep(40);
+      __nanosleep(it < 4096 ? 40 : 400);
     }
     if (!ok) { s_late = 1; atomicExch(&g_peer_error, 1); }
   }
