@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "vllm_quant_kernels", "libvqk.so")
 OBJ = os.path.join(HERE, "build")
-SOURCES = ["api.cu", "quantize.cu", "lm_head_stream.cu", "lm_head_tma.cu", "lm_head_umma.cu", "lm_head_umma_mx.cu", "sampler.cu"]
+SOURCES = ["api.cu", "quantize.cu", "lm_head_stream.cu", "lm_head_umma.cu", "lm_head_umma_mx.cu", "sampler.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -122,8 +122,8 @@ extern "C" const char* vqk_strerror(int s) {
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int vqk_device_error(void) {
-  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag(), d = peer_error_flag();
-  return (a < 0 || b < 0 || c < 0 || d < 0) ? -1 : (a | b | c | d);
+  const int b = umma_error_flag(), c = umma_mx_error_flag(), d = peer_error_flag();
+  return (b < 0 || c < 0 || d < 0) ? -1 : (b | c | d);
 }
 
 extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
@@ -186,21 +186,18 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   const int mode = h->mode;
   // Kernel choice: the register-streaming kernel for decode batches, the tcgen05 tensor-core
   // kernel once the batch is large enough that re-streaming the weights per 32 columns (or the
-  // warp-MMA rate) would cost more.  VQK_LM_HEAD_KERNEL = stream | umma | tma pins one (A/B runs;
-  // tma is the bulk-copy pipeline variant of the streaming kernel).
+  // warp-MMA rate) would cost more.  VQK_LM_HEAD_KERNEL = stream | umma pins one (A/B runs).
   const char* kenv = getenv("VQK_LM_HEAD_KERNEL");
-  const bool want_tma = kenv && !strcmp(kenv, "tma");
   const bool want_umma = kenv && !strcmp(kenv, "umma");
   const bool want_stream = kenv && !strcmp(kenv, "stream");
-  int maxcols = want_tma ? tma_max_cols(mode, (int)h->H) : 0;
-  const bool use_tma = want_tma && maxcols > 0 && (h->V % 16 == 0) && !((uintptr_t)h->scales & 15);
+  int maxcols = 0;
   const bool mx_mode = (mode == VQK_MODE_MXFP8 || mode == VQK_MODE_MXFP4);
   const int umma_cols = mx_mode ? umma_mx_max_cols(mode, (int)h->H) : umma_max_cols(mode, (int)h->H);
   // the block-scaled modes take the tensor-core path at every batch size: the hardware applies
   // the E8M0 scales, which the register kernel has to do with ALU work per element
-  const bool use_umma = !use_tma && !want_stream && umma_cols > 0 && (want_umma || mx_mode || B > kUmmaMinBatch);
+  const bool use_umma = !want_stream && umma_cols > 0 && (want_umma || mx_mode || B > kUmmaMinBatch);
   if (use_umma) maxcols = umma_cols;
-  else if (!use_tma) maxcols = stream_max_cols(mode, (int)h->H);
+  else maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
 
   LmHeadWs ws = carve_lm_head(workspace, mode, h->V, h->H, B, sp != nullptr, nslices);
@@ -253,7 +250,6 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
       }
     }
     rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
-         : use_tma ? launch_lm_head_tma(mode, p, sms, st)
                    : launch_lm_head_stream(mode, p, sms, st);
     if (rc) return rc;
   }

@@ -31,10 +31,6 @@ size_t stream_smem_bytes(int mode, int K, int NT);
 int stream_max_cols(int mode, int K);  // batch columns one launch can take (0: K too large)
 int launch_lm_head_stream(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
 
-// lm_head_tma.cu: bulk-copy pipeline; needs V % 16 == 0, 16-byte aligned rows and scales
-int tma_max_cols(int mode, int K);     // batch columns per launch (0: shape not covered)
-int launch_lm_head_tma(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
-int stream_error_flag();               // 1 if a bounded wait inside the kernel ever expired (synchronises)
 
 // lm_head_umma.cu: tcgen05 tensor-core kernel for larger batches (FP8, W8A8; K % 128 == 0)
 int umma_max_cols(int mode, int K);    // 256, or 0 when the mode / shape is not covered
