@@ -433,9 +433,25 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   float tau = m.thr;
   if (m.top_k > 0) {
     const int ns = p.nslices;
-    for (int s = tid; s < ns; s += blockDim.x) s_sm[s] = p.slice_max[(long long)b * ns + s];
-    __syncthreads();
-    tau = smem_kth_largest(s_sm, ns, m.top_k, s_full.hist, s_full.bc);
+    int nonempty = 0;  // slices that hold at least one finite logit
+    for (int s0 = 0; s0 < ns; s0 += blockDim.x) {  // ns is uniform: every thread runs every round
+      const int s = s0 + tid;
+      bool finite = false;
+      if (s < ns) {
+        const float v = p.slice_max[(long long)b * ns + s];
+        s_sm[s] = v;
+        finite = v > -INFINITY;
+      }
+      nonempty += __syncthreads_count(finite);
+    }
+    if (nonempty >= m.top_k) {
+      tau = smem_kth_largest(s_sm, ns, m.top_k, s_full.hist, s_full.bc);
+    } else {
+      // Fewer slices with data than k (a short vocab shard under a wide-tile kernel): the k-th
+      // largest slice maximum is -inf and would admit the whole row.  Take the exact k-th
+      // largest logit of the row instead (every CTA of the cluster computes the same value).
+      tau = p.V >= m.top_k ? radix_kth_largest(row, p.V, m.top_k, s_full.hist, s_full.bc) : -INFINITY;
+    }
   }
   cluster.sync();  // rank 0's candidate counter is zero before anybody pushes
 
