@@ -693,6 +693,11 @@ int launch_select(const SelectParams& p, cudaStream_t st) {
   const size_t share = (size_t)kSelThreads * kSelPreload * 16;
   int cs = 1;
   while (cs < kClusterSize && (size_t)p.V * esz > share * cs) cs <<= 1;
+  // ... and no more CTAs in total than SMs (one 1024-thread CTA fits an SM): every CTA of a cluster repeats the
+  // threshold search of its row, so with many rows narrow clusters (longer scans, fewer
+  // repeats) finish sooner
+  const int budget = device_sm_count();
+  while (cs > 1 && (long long)cs * p.B > budget) cs >>= 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)cs, (unsigned)p.B);
   cfg.blockDim = dim3(kSelThreads);
