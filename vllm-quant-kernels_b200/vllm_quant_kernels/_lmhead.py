@@ -167,6 +167,8 @@ class LMHeadShard:
         self.V = q.shape[0]
         self.H = int(K) if K is not None else (q.shape[1] * 2 if mode == "mxfp4" else q.shape[1])
         self.device = q.device
+        self._dev_index = q.device.index if q.device.index is not None else torch.cuda.current_device()
+        self._ws_bytes = {}
         h = ctypes.c_void_p()
         _ffi.check(_ffi.lib().vqk_lm_head_create(MODES[mode], q.data_ptr(), scales.data_ptr(), self.V, self.H,
                                                  ctypes.byref(h)))
@@ -199,22 +201,33 @@ class LMHeadShard:
         return x
 
     def _ws(self, B: int, sample: bool):
-        with torch.cuda.device(self.device):
-            n = _ffi.lib().vqk_lm_head_workspace_bytes(self._h, B, 1 if sample else 0)
-        if n < 0:
-            _ffi.check(int(n))
-        return _WS.get(self.device, int(n)), int(n)
+        key = (B, sample)
+        n = self._ws_bytes.get(key)
+        if n is None:  # the size depends on (B, sample) only: ask the library once
+            with torch.cuda.device(self.device):
+                n = int(_ffi.lib().vqk_lm_head_workspace_bytes(self._h, B, 1 if sample else 0))
+            if n < 0:
+                _ffi.check(n)
+            self._ws_bytes[key] = n
+        return _WS.get(self.device, n), n
 
     def _forward(self, x, bias, logits, sp, tokens, scores, records):
         B = x.shape[0]
         ws, n = self._ws(B, sp is not None)
         spc = sp.to_c(B, self.V) if sp is not None else None
-        with torch.cuda.device(self.device):
+
+        def call():
             _ffi.check(_ffi.lib().vqk_lm_head_forward(
                 self._h, x.data_ptr(), _DT[x.dtype], B, x.stride(0), _ptr(bias),
                 _ptr(logits), logits.stride(0) if logits is not None else 0,
                 ctypes.byref(spc) if spc is not None else None,
                 _ptr(tokens), _ptr(scores), _ptr(records), ws.data_ptr(), n, _stream(x)))
+
+        if torch.cuda.current_device() == self._dev_index:  # decode loop: no device switch to pay for
+            call()
+        else:
+            with torch.cuda.device(self.device):
+                call()
 
     def logits(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """fp16 logits [B, V] (reference: every `_*_forward` launcher, _quant.py:399-643)."""
