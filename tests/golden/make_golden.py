@@ -1,8 +1,8 @@
 """Generate the golden vectors in this directory by RUNNING THE REFERENCE's own
-Python code on CPU.  Needs the reference checkout (path in $VQK_REFERENCE,
-default /root/reference), torch, triton and vllm importable; no GPU.
+Python code on CPU.  Needs a checkout of the reference (himikk/vllm-quant-kernels;
+its path in $VQK_REFERENCE), torch, triton and vllm importable; no GPU.
 
-    python tests/golden/make_golden.py
+    VQK_REFERENCE=<reference checkout> python tests/golden/make_golden.py
 
 What runs:
   * the reference's torch quantizers and `_init_*` methods, unmodified, on CPU
@@ -27,7 +27,9 @@ import sys
 import types
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = os.environ.get("VQK_REFERENCE", "/root/reference")
+REF = os.environ.get("VQK_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "src")):
+    raise SystemExit("set VQK_REFERENCE to a checkout of the reference (the directory that holds src/ and tests/)")
 sys.path.insert(0, os.path.join(REF, "src"))
 sys.path.insert(0, os.path.join(REF, "tests"))
 
