@@ -195,7 +195,10 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   const int umma_cols = mx_mode ? umma_mx_max_cols(mode, (int)h->H) : umma_max_cols(mode, (int)h->H);
   // the block-scaled modes take the tensor-core path at every batch size: the hardware applies
   // the E8M0 scales, which the register kernel has to do with ALU work per element
-  const bool use_umma = !want_stream && umma_cols > 0 && (want_umma || mx_mode || B > kUmmaMinBatch);
+  // the tensor maps want aligned operands (32 bytes for the packed 4-bit rows); anything else
+  // stays on the streaming kernel, which only needs 16-byte aligned rows
+  const bool umma_aligned = (((uintptr_t)h->q & (mx_mode ? 31 : 15)) == 0) && (!mx_mode || ((uintptr_t)h->scales & 3) == 0);
+  const bool use_umma = !want_stream && umma_cols > 0 && umma_aligned && (want_umma || mx_mode || B > kUmmaMinBatch);
   if (use_umma) maxcols = umma_cols;
   else maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
