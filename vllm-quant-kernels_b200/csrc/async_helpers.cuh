@@ -47,6 +47,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   atomicExch(&g_stream_error, 1);
   return false;
 }
+// Drain of a producer's own copies before its CTA exits: wait, with a limit and whatever the
+// abort flag says, until the barrier phase that the copy completes has passed.  On the normal
+// path the consumer has already waited for it and this returns at once.
+__device__ __forceinline__ bool mbar_drain(uint64_t* bar, uint32_t parity) {
+  for (uint32_t it = 0; it < (1u << 20); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
 // warp-uniform form: every lane polls, the warp proceeds only if every lane got through
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;

@@ -61,7 +61,8 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NI * S * geo.stage_bytes);
   uint64_t* tfull = bars;            // [NI * 2]
   uint64_t* tempty = bars + 2 * NI;  // [NI * 2]
-  uint64_t* lane_bars = bars + 4 * NI;
+  uint64_t* drained = bars + 4 * NI;   // [NI]: an issuer's last commit, waited for before the CTA exits
+  uint64_t* lane_bars = bars + 5 * NI;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(lane_bars + NI * kPerLane);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   RowMeta* meta = reinterpret_cast<RowMeta*>(bars + 128);
@@ -74,6 +75,7 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
 
   if (tid == 0) {
     for (int i = 0; i < 2 * NI; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int l = 0; l < NI; ++l) mbar_init(&drained[l], 1);
     for (int l = 0; l < NI; ++l)
       for (int s = 0; s < S; ++s) { mbar_init(&lane_bars[l * kPerLane + s], 1); mbar_init(&lane_bars[l * kPerLane + kMaxStages + s], 1); }
     *abort_flag = 0;
@@ -104,7 +106,7 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
       uint64_t* full = lane_bars + l * kPerLane;
       uint64_t* empty = full + kMaxStages;
       uint8_t* my = smem + (size_t)l * S * geo.stage_bytes;
-      int s = 0;
+      int s = 0, issued = 0;
       uint32_t ph = 0;
       bool ok = true;
       for (int n = l; n < mytiles && ok; n += NI) {
@@ -115,9 +117,13 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
           mbar_expect_tx(&full[s], (uint32_t)geo.stage_bytes);
           tma_load_2d(sa, &mapA, kb * BK, row0, &full[s]);
           tma_load_2d(sa + BM * BK, &mapB, kb * BK, 0, &full[s]);
+          ++issued;
           if (++s == S) { s = 0; ph ^= 1u; }
         }
       }
+      // no copy of this thread may still be in flight when the CTA exits: the last min(issued, S)
+      // stages are the only ones that can be (on the normal path they have all been consumed)
+      for (int i = issued > S ? issued - S : 0; i < issued; ++i) mbar_drain(&full[i % S], (uint32_t)(i / S) & 1u);
     }
   } else if (warp < 2 * NI) {
     // ================================ MMA issuers =======================================
@@ -151,6 +157,9 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
         }
         if (ok) umma_commit(&tfull[acc]);  // accumulator complete
       }
+      // nothing this thread issued may still be running when the CTA frees its TMEM and exits
+      umma_commit(&drained[l]);
+      mbar_drain(&drained[l], 0);
     }
   } else {
     umma_epilogue<INT8 ? 1 : 0, BN, NI>(p, warp, lane, tmem_base, tfull, tempty, abort_flag, meta, sstate, ntiles);
