@@ -353,11 +353,14 @@ __device__ float smem_kth_largest(const float* v, int n, int k, unsigned int* hi
 // loads into registers), then the cluster rank-counts the slice maxima for tau while those loads
 // land; candidates >= tau go straight into rank 0's shared memory through DSMEM atomics, and
 // rank 0 resolves them (or runs the exact full-row pass when the row does not fit).
-constexpr int kSelThreads = 1024;
-constexpr int kSelPreload = 4;  // 16-byte vectors per thread fetched before tau is known
+// THREADS = 512 for a few rows (the kernel is a chain of block barriers there, which cost less with
+// 16 warps), 1024 for many rows (each CTA then scans a long share of its row and wants the loads
+// of 32 warps in flight).  Either way a CTA preloads 64 KB of its share before tau is known.
+constexpr int kSelShare = 65536;
 
-template <typename T>
+template <typename T, int kSelThreads>
 __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
+  constexpr int kSelPreload = kSelShare / 16 / kSelThreads;  // 16-byte vectors per thread fetched before tau is known
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (int)cluster.block_rank();
   const int csize = (int)cluster.num_blocks();  // 1, 2, 4 or 8: chosen by the launcher from the row length
@@ -686,11 +689,11 @@ int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V,
 
 int launch_select(const SelectParams& p, cudaStream_t st) {
   if (p.B == 0) return VQK_OK;
-  // CTAs per row: enough that a CTA's share fits the registers it preloads (1024 threads x
-  // kSelPreload x 16 bytes), at most kClusterSize; short rows (a vocab shard) take one CTA and
+  // CTAs per row: enough that a CTA's share fits the registers it preloads (kSelShare bytes),
+  // at most kClusterSize; short rows (a vocab shard) take one CTA and
   // skip the cluster traffic altogether
   const size_t esz = p.dtype == VQK_F32 ? 4 : 2;
-  const size_t share = (size_t)kSelThreads * kSelPreload * 16;
+  const size_t share = kSelShare;
   int cs = 1;
   while (cs < kClusterSize && (size_t)p.V * esz > share * cs) cs <<= 1;
   // ... and no more CTAs in total than SMs (one 1024-thread CTA fits an SM): every CTA of a cluster repeats the
@@ -700,7 +703,8 @@ int launch_select(const SelectParams& p, cudaStream_t st) {
   while (cs > 1 && (long long)cs * p.B > budget) cs >>= 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)cs, (unsigned)p.B);
-  cfg.blockDim = dim3(kSelThreads);
+  const bool narrow = (long long)cs * p.B <= 64;  // few CTAs in all: latency, not throughput, decides
+  cfg.blockDim = dim3(narrow ? 512 : 1024);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -711,7 +715,11 @@ int launch_select(const SelectParams& p, cudaStream_t st) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t le = cudaSuccess;
-  VQK_DISPATCH_DTYPE(p.dtype, (le = cudaLaunchKernelEx(&cfg, k_select<T>, p)));
+  if (narrow) {
+    VQK_DISPATCH_DTYPE(p.dtype, (le = cudaLaunchKernelEx(&cfg, k_select<T, 512>, p)));
+  } else {
+    VQK_DISPATCH_DTYPE(p.dtype, (le = cudaLaunchKernelEx(&cfg, k_select<T, 1024>, p)));
+  }
   VQK_CUDA(le);
   return VQK_OK;
 }
