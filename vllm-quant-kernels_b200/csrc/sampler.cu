@@ -2,9 +2,10 @@
 //
 // Pass 1 (here k_slice_pass, or the lm_head epilogue) reduces every 256-column slice of a row
 // to either a Gumbel winner (rows without top-k/top-p) or its maximum raw logit (rows with).
-// Pass 2 (k_select, one 8-CTA cluster per row) turns the slice maxima into a lower bound tau
+// Pass 2 (k_select, a cluster of 1 to 8 CTAs per row) turns the slice maxima into a lower bound tau
 // on the k-th largest logit (the k-th largest slice maximum: k disjoint slices each hold a
-// value >= it), re-reads the row, keeps the few columns >= tau, and resolves them exactly:
+// value >= it; the exact k-th largest logit when fewer than k slices hold data), re-reads the
+// row, keeps the few columns >= tau, and resolves them exactly:
 // top-k with ties kept (>=, as _sampler_kernels.py:88-90), vLLM's top-p, Philox noise only
 // for the survivors.  Rows that do not fit (top-p without top-k, more ties than the candidate
 // buffer) go through fullrow_resolve, an exact radix-select pass over the whole row.
@@ -18,7 +19,6 @@ namespace vqk {
 
 constexpr int kClusterSize = 8;
 constexpr int kMaxSlices = 2048;
-constexpr int kLocalCap = 512;    // candidates one CTA of the cluster may collect
 constexpr int kGlobalCap = 1024;  // candidates resolved per row
 constexpr double kMassScale = 1099511627776.0;  // 2^40 fixed point for probability mass
 
@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (int)cluster.block_rank();
   const int csize = (int)cluster.num_blocks();  // 1, 2, 4 or 8: chosen by the launcher from the row length
-  const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = blockIdx.y, tid = threadIdx.x;
   const RowMeta m = decode_row(p.sp, b);
   const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
 
