@@ -51,6 +51,23 @@ def test_bad_arguments_are_rejected_without_a_device():
     assert L.vqk_comm_create(None, 0, 1, ctypes.byref(h)) == -1
 
 
+def test_peer_exchange_rejects_bad_arguments_without_a_device():
+    """vqk_peer_*: argument errors come back before any CUDA call; destroying nothing is fine."""
+    from vllm_quant_kernels import _ffi
+    L = _ffi.lib()
+    h = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(_ffi.PEER_HANDLE_BYTES)
+    assert L.vqk_peer_create(1, 1, 16, ctypes.byref(h), handle) == -1          # rank >= nranks
+    assert L.vqk_peer_create(0, 9, 16, ctypes.byref(h), handle) == -1          # more than 8 ranks
+    assert L.vqk_peer_create(0, 2, 0, ctypes.byref(h), handle) == -1           # no rows
+    assert L.vqk_peer_create(0, 2, 16, ctypes.byref(h), None) == -1            # nowhere to put the handle
+    assert L.vqk_peer_connect(None, handle) == -1
+    sp = _ffi.SampleParams()
+    assert L.vqk_peer_exchange_finalize(None, 256, 1, ctypes.byref(sp), 256, None, None) == -1
+    assert L.vqk_peer_destroy(None) == 0
+    assert _ffi.PEER_HANDLE_BYTES == 64 and _ffi.PEER_MAX_RANKS == 8
+
+
 def test_missing_library_is_a_loud_error(monkeypatch):
     from vllm_quant_kernels import _ffi
     monkeypatch.setattr(_ffi, "_lib", None)
