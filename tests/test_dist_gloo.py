@@ -93,3 +93,36 @@ def test_two_rank_record_exchange_and_merge(tmp_path):
             toks = [t for r in recs for _, t in r["cands"]]
             tok, _ = OS.resolve_candidates(vals, toks, T[i], seeds[i], int(top_k[i]), float(top_p[i]))
         assert tok == ref["tokens"][i], (i, tok, ref["tokens"][i])
+
+
+def _peer_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "vllm-quant-kernels_b200"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from vllm_quant_kernels._dist import VqkPeer
+        msg = "no error"
+        try:
+            VqkPeer(rank, world, max_rows=4, device="cuda:0")
+        except RuntimeError as exc:
+            msg = str(exc)
+        with open(f"{out}.{rank}", "w") as f:
+            f.write(msg)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_peer_setup_fails_on_every_rank_together(tmp_path):
+    """Without a GPU the landing buffer cannot be created.  Every rank must still walk through
+    the same collectives and raise the same error: a rank failing on its own would leave its
+    peers blocked in the handle exchange."""
+    if torch.cuda.is_available():
+        pytest.skip("the failure path under test needs a machine without a GPU")
+    out = str(tmp_path / "peer")
+    mp.spawn(_peer_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    msgs = [open(f"{out}.{r}").read() for r in range(2)]
+    assert all(m.startswith("peer-memory exchange unavailable") for m in msgs), msgs
+    assert "rank 0" in msgs[1] and "rank 1" in msgs[0]

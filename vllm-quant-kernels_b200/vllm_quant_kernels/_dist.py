@@ -83,13 +83,29 @@ class VqkPeer:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         h = ctypes.c_void_p()
         mine = ctypes.create_string_buffer(_ffi.PEER_HANDLE_BYTES)
-        with torch.cuda.device(self.device):
-            _ffi.check(L.vqk_peer_create(rank, world, max_rows, ctypes.byref(h), mine))
-        self._h = h
-        handles = [None] * world
-        dist.all_gather_object(handles, mine.raw, group=group)
-        with torch.cuda.device(self.device):
-            _ffi.check(L.vqk_peer_connect(self._h, b"".join(handles)))
+        # Every rank takes part in every collective below whatever happened locally, and all
+        # ranks raise together: a rank that failed alone would leave the others waiting.
+        err = None
+        try:
+            with torch.cuda.device(self.device):
+                _ffi.check(L.vqk_peer_create(rank, world, max_rows, ctypes.byref(h), mine))
+        except Exception as exc:  # noqa: BLE001
+            err = f"rank {rank}: create: {exc}"
+        self._h = h if err is None else None
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (err, mine.raw), group=group)
+        if err is None and all(e is None for e, _ in gathered):
+            try:
+                with torch.cuda.device(self.device):
+                    _ffi.check(L.vqk_peer_connect(self._h, b"".join(hb for _, hb in gathered)))
+            except Exception as exc:  # noqa: BLE001
+                err = f"rank {rank}: connect: {exc}"
+        errs = [None] * world
+        dist.all_gather_object(errs, err if err is not None else next((e for e, _ in gathered if e), None), group=group)
+        bad = [e for e in errs if e]
+        if bad:
+            self.close()
+            raise RuntimeError("peer-memory exchange unavailable: " + "; ".join(sorted(set(bad))))
         dist.barrier(group=group)  # nobody pushes before every rank has mapped every buffer
         self.rank, self.world, self.max_rows = rank, world, max_rows
 
