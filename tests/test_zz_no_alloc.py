@@ -70,6 +70,12 @@ def test_static_scratch_sampler_matches_workspace_sampler_twice():
         assert torch.equal(tok, tok_ref), (tok.tolist(), tok_ref.tolist())
         assert torch.equal(sc, sc_ref)
         assert int(tok.min()) >= 0 and int(tok.max()) < V
+        # ... and to the CPU oracle on the same logits, so the check does not lean on vqk_sample alone
+        want = OS.sample(logits.float().cpu().numpy(), a["T"].cpu().numpy(), a["seeds"].cpu().numpy(),
+                         top_k=a["k"].cpu().numpy(), top_p=a["p"].cpu().numpy())
+        decided = (want["margin"] > 1e-4) & (want["p_margin"] > 2e-6)
+        assert decided.mean() >= 0.5
+        assert (tok.cpu().numpy()[decided] == want["tokens"][decided]).all()
 
 
 def test_static_scratch_sampler_rejects_sizes_beyond_its_maximum():

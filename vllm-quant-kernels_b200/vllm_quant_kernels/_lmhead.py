@@ -133,17 +133,25 @@ class SamplingArgs:
 
 
 class _Workspace:
-    """One growing byte buffer per device; torch owns the memory."""
+    """Scratch buffers per device (one instance per lm_head shard, one for the stand-alone
+    sampler entry points).  A buffer that was
+    handed out is never freed or replaced (a CUDA graph captured earlier keeps its raw pointer):
+    a larger request adds a buffer, a smaller one reuses the smallest that fits.  Calls that share
+    a buffer must run on one stream."""
 
     def __init__(self):
-        self._buf = {}
+        self._bufs = {}
 
     def get(self, dev: torch.device, nbytes: int) -> torch.Tensor:
         key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
-        b = self._buf.get(key)
-        if b is None or b.numel() < nbytes:
-            b = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
-            self._buf[key] = b
+        bufs = self._bufs.setdefault(key, [])
+        fit = [b for b in bufs if b.numel() >= nbytes]
+        if fit:
+            return min(fit, key=lambda b: b.numel())
+        # grow geometrically: a run of ever larger requests then holds at most twice the largest
+        largest = max((b.numel() for b in bufs), default=0)
+        b = torch.empty(max(nbytes, 2 * largest, 1), dtype=torch.uint8, device=dev)
+        bufs.append(b)
         return b
 
 
@@ -169,6 +177,7 @@ class LMHeadShard:
         self.device = q.device
         self._dev_index = q.device.index if q.device.index is not None else torch.cuda.current_device()
         self._ws_bytes = {}
+        self._wsp = _Workspace()  # this shard's own scratch, kept for the shard's lifetime
         h = ctypes.c_void_p()
         _ffi.check(_ffi.lib().vqk_lm_head_create(MODES[mode], q.data_ptr(), scales.data_ptr(), self.V, self.H,
                                                  ctypes.byref(h)))
@@ -201,6 +210,10 @@ class LMHeadShard:
         return x
 
     def _ws(self, B: int, sample: bool):
+        """Scratch of this shard for batch B.  Every shard owns its buffers and never frees one
+        it handed out, so a step captured in a CUDA graph never sees its scratch replaced by a
+        later, larger call, and two shards never share scratch.  Calls on ONE shard share
+        buffers: keep them on one stream."""
         key = (B, sample)
         n = self._ws_bytes.get(key)
         if n is None:  # the size depends on (B, sample) only: ask the library once
@@ -209,7 +222,7 @@ class LMHeadShard:
             if n < 0:
                 _ffi.check(n)
             self._ws_bytes[key] = n
-        return _WS.get(self.device, n), n
+        return self._wsp.get(self.device, n), n
 
     def _forward(self, x, bias, logits, sp, tokens, scores, records):
         B = x.shape[0]

@@ -233,11 +233,28 @@ class QuantizedLogitsProcessor(LogitsProcessor):
     def sample_fused(self, hidden_states, lm_head, sampling_args: "_lmhead.SamplingArgs", embedding_bias=None):
         """lm_head and sampler in one pass: (tokens int64 [B], scores fp32 [B]); the
         logits are never written to memory unless a row needs top-k / top-p.  Not part
-        of the reference's surface; vLLM's runner reaches it only if it is patched to."""
+        of the reference's surface; vLLM's runner reaches it only if it is patched to.
+
+        Samples over the first `org_vocab_size` rows only (vLLM pads the vocabulary; a padding
+        row quantizes to zero and could otherwise win when the real logits are negative).
+        Single shard: with tensor parallelism the vocab shards of the ranks have to be merged,
+        which is `_dist.VocabShardedLMHead`'s job, so TP > 1 raises here."""
         if not hasattr(self, "_int8_initialized"):
             self._int8_initialized = True
             self._init_int8(lm_head)
         sh = getattr(lm_head, "_vqk_shard", None)
         if sh is None:
             raise RuntimeError("lm_head is not quantized (see the eligibility rules of _init_int8)")
+        if _tp_world_size() > 1:
+            raise RuntimeError("sample_fused samples one vocab shard; with tensor parallelism use "
+                               "vllm_quant_kernels._dist.VocabShardedLMHead with this rank's vocab_start")
+        org = getattr(self, "org_vocab_size", None)
+        if org is not None and 0 < org < sh.V:
+            fs = getattr(lm_head, "_vqk_fused_shard", None)
+            if fs is None or fs.V != org or fs.q.data_ptr() != sh.q.data_ptr():
+                fs = _lmhead.LMHeadShard(sh.mode, sh.q[:org], sh.scales[:org], sh.H)
+                lm_head._vqk_fused_shard = fs
+            sh = fs
+        if embedding_bias is not None and embedding_bias.shape[-1] > sh.V:
+            embedding_bias = embedding_bias[..., :sh.V]
         return sh.sample(hidden_states, sampling_args, embedding_bias)
