@@ -59,6 +59,9 @@ int vqk_last_cuda_error(void);
  * (the kernel then drained and left its outputs undefined), 0 if not, -1 on a CUDA error.
  * For tests and post-mortems; not for the hot path. */
 int vqk_device_error(void);
+/* Synchronises the device and puts the flag vqk_device_error reports back to 0 (after a wait ran
+ * out the flag would otherwise stay set for the life of the process). */
+int vqk_device_error_clear(void);
 
 /* ---------------------------------------------------------------------------
  * Offline weight quantisation.  Replaces the torch code in
@@ -127,7 +130,9 @@ typedef struct {
 typedef struct vqk_lm_head vqk_lm_head;
 
 /* Describe one vocab shard: quantized rows [V, H] and their scales in the layouts
- * of vqk_quantize_weight.  Host-side object; holds no device memory. */
+ * of vqk_quantize_weight.  Host-side object; allocates no device memory (it is given one of a
+ * few counters that live inside the library).  One call at a time per handle: calls on the same
+ * handle must be ordered on one stream. */
 int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
                        vqk_lm_head** out);
 int vqk_lm_head_destroy(vqk_lm_head* h);
@@ -141,7 +146,10 @@ int64_t vqk_lm_head_workspace_bytes(const vqk_lm_head* h, int64_t B, int sample)
  *   bias     fp16 [V] or NULL
  *   logits   fp16 [B, ld_logits] or NULL (not written when NULL)
  *   sp       NULL -> logits only.  Otherwise the sampler runs on the fp16-rounded
- *            logits inside the same pass:
+ *            logits inside the same pass (up to 16 rows: inside the same KERNEL, whose last
+ *            CTA resolves the rows from per-slice lists of the largest logits; a row those
+ *            lists cannot decide, and every top-k / top-p row of a larger batch, is resolved
+ *            by a second kernel from its fp16 logits row, kept in the workspace):
  *              tokens/scores non-NULL -> final int64 token ids / fp32 winning scores
  *                                        (single shard: vocab_total == V);
  *              records non-NULL       -> [B] exchange records for a sharded step, to
@@ -157,6 +165,11 @@ int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, int64_t B, i
  * `stop` right after its weight-streaming kernel launch(es) on the call's stream, so a
  * benchmark can time that kernel in place.  Pass NULLs to switch it off. */
 int vqk_lm_head_set_kernel_events(vqk_lm_head* h, void* start_event, void* stop_event);
+/* Measurement aid (no counterpart in the reference): a device buffer of gridDim x 16 uint64
+ * (148 x 16 on B200) in which CTA c of the streaming and block-scaled lm_head kernels leaves
+ * %globaltimer stamps at [c][0] entry, [c][1] weight stream done, [c][2] slice results written,
+ * and the CTA that ran the sampler tail [c][3] tail start, [c][4] tail end, [c][5..] phases of row 0.  NULL switches it off. */
+int vqk_lm_head_set_debug_times(vqk_lm_head* h, void* device_buffer);
 
 /* ---------------------------------------------------------------------------
  * Stand-alone sampler on materialised logits.  Replaces fused_gumbel_sample
@@ -217,15 +230,28 @@ int vqk_comm_destroy(vqk_comm* c);
 /* ---------------------------------------------------------------------------
  * The same exchange without NCCL, fused with the merge (no counterpart in the
  * reference): every rank (one process per GPU, all on one node) owns a landing
- * buffer that its peers map through CUDA IPC; ONE kernel copies this rank's records
- * into every rank's buffer with plain peer stores over NVLink, publishes a per-row
- * step number, waits (bounded: a peer that never arrives gives token -1 and sets
- * vqk_device_error) for the other ranks' records of the same step and merges them.
- * All ranks must make the same sequence of calls with the same B.  Safe to capture
- * in a CUDA graph (the step number lives in device memory).
- *   vqk_peer_create   allocates the landing buffer (not on the hot path) and returns
- *                     the handle to hand to every other rank (any transport).
- *   vqk_peer_connect  takes all ranks' handles, rank-major, own one included.
+ * buffer that its peers map through CUDA IPC.  The warp that holds a row's record
+ * stores it into every rank's buffer with plain 8-byte peer stores over NVLink (every
+ * word is self-validating, so there is no flag and no fence), waits (bounded: a peer
+ * that never arrives gives token -1 and sets vqk_device_error) for the other ranks'
+ * records of the same step, merges them and hands the slots back.  No multicast, no
+ * remote loads.  All ranks must make the same sequence of calls with the same B.  Safe
+ * to capture in a CUDA graph (the step number lives in device memory).
+ *   vqk_peer_create            allocates the landing buffer (not on the hot path) and returns
+ *                              the handle to hand to every other rank (any transport).
+ *   vqk_peer_connect           takes all ranks' handles, rank-major, own one included.
+ *   vqk_peer_connect_pointers  the same for landing buffers the caller can already address
+ *                              (several vqk_peer in one process: vqk_peer_local_buffer of each).
+ *   vqk_peer_set_wait_limit    bound of every wait in polls (default about a second).
+ *   vqk_lm_head_step_sharded   the whole sharded step in one call: this rank's lm_head shard,
+ *                              its sampling stage, the exchange and the merge.  Up to 16 rows
+ *                              ALL of it runs inside the lm_head kernel (its last CTA: one warp
+ *                              per row); beyond, and for rows the lists cannot decide, the
+ *                              full-row sampler kernel behind it does the exchange.  sp carries
+ *                              this rank's vocab_offset and the global vocab_total; tokens and
+ *                              scores are the merged result, identical on every rank.
+ *   vqk_peer_exchange_finalize exchange + merge of records computed earlier (vqk_lm_head_forward
+ *                              or vqk_sample with `records`), as a kernel of its own.
  * ------------------------------------------------------------------------- */
 typedef struct vqk_peer vqk_peer;
 #define VQK_PEER_HANDLE_BYTES 64
@@ -233,6 +259,13 @@ typedef struct vqk_peer vqk_peer;
 int vqk_peer_create(int rank, int nranks, int64_t max_rows, vqk_peer** out,
                     void* handle_out_host /* VQK_PEER_HANDLE_BYTES */);
 int vqk_peer_connect(vqk_peer* p, const void* all_handles_host /* nranks * VQK_PEER_HANDLE_BYTES */);
+int vqk_peer_connect_pointers(vqk_peer* p, void* const* buffers_host /* nranks device pointers; own entry ignored */);
+void* vqk_peer_local_buffer(vqk_peer* p);
+int vqk_peer_set_wait_limit(vqk_peer* p, int64_t polls);
+int64_t vqk_lm_head_step_sharded_workspace_bytes(const vqk_lm_head* h, int64_t B);
+int vqk_lm_head_step_sharded(vqk_lm_head* h, vqk_peer* peer, const void* x, int x_dtype, int64_t B, int64_t ldx,
+                             const void* bias, const vqk_sample_params* sp, int64_t* tokens, float* scores,
+                             void* workspace, int64_t workspace_bytes, void* stream);
 int vqk_peer_exchange_finalize(vqk_peer* p, const void* records /* [B, VQK_RECORD_BYTES] device */, int64_t B,
                                const vqk_sample_params* sp, int64_t* tokens, float* scores, void* stream);
 int vqk_peer_destroy(vqk_peer* p);

@@ -57,12 +57,39 @@ def main():
                 assert torch.equal(tok, ref_tok), (rank, mode, list(kw), tok.tolist(), ref_tok.tolist())
                 assert torch.equal(sc, ref_sc)
             ph = VocabShardedLMHead(mine, a, V, peer=peer)
-            for _ in range(3):  # both parities of the landing buffer
+            for _ in range(3):  # both parities of the landing buffer; the whole step is one library call
                 tok, sc = ph.step(x, sp)
                 torch.cuda.synchronize()
                 assert torch.equal(tok, ref_tok), ("peer", rank, mode, list(kw), tok.tolist(), ref_tok.tolist(),
                                                    "device_error", _ffi.lib().vqk_device_error())
                 assert torch.equal(sc, ref_sc)
+            # the exchange as a kernel of its own, fed the records of the separate lm_head call
+            rec = mine.shard_records(x, ph.local_args(sp))
+            tok, sc = peer.exchange_finalize(rec, ph.local_args(sp))
+            torch.cuda.synchronize()
+            assert torch.equal(tok, ref_tok) and torch.equal(sc, ref_sc), ("peer records", rank, mode, list(kw))
+        # a batch above 16 rows: the full-row sampler kernel does the exchange
+        xb = torch.randn(24, H, generator=torch.Generator().manual_seed(11)).half().to(dev)
+        rngb = np.random.default_rng(5)
+        Tb = torch.from_numpy(rngb.uniform(0.5, 1.5, 24).astype(np.float32)).to(dev)
+        sb = torch.from_numpy(rngb.integers(0, 2**31 - 1, 24).astype(np.int32)).to(dev)
+        kb = torch.full((24,), 40, dtype=torch.int32, device=dev)
+        pb = torch.full((24,), 0.85, dtype=torch.float32, device=dev)
+        spb = LH.SamplingArgs(Tb, sb, kb, pb, None, 0, V)
+        ref_tok, ref_sc = full.sample(xb, spb)
+        tok, sc = VocabShardedLMHead(mine, a, V, peer=peer).step(xb, spb)
+        torch.cuda.synchronize()
+        assert torch.equal(tok, ref_tok) and torch.equal(sc, ref_sc), ("peer batch 24", rank, mode)
+        # rows the records cannot carry (top-p without top-k): -1 from the merge, exact after the rerun
+        spp = args(top_p=np.full(B, 0.8, np.float32))
+        ref_tok, ref_sc = full.sample(x, spp)
+        for c, ph2 in ((comm, VocabShardedLMHead(mine, a, V, comm=comm)), (None, VocabShardedLMHead(mine, a, V, peer=peer))):
+            tok, _ = ph2.step(x, spp)
+            torch.cuda.synchronize()
+            assert (tok[1:] == -1).all() and tok[0] == ref_tok[0], ("unresolved rows", rank, tok.tolist())
+            tok, sc = ph2.step(x, spp, unresolved="rerun")
+            torch.cuda.synchronize()
+            assert torch.equal(tok, ref_tok) and torch.equal(sc, ref_sc), ("rerun", rank, mode, tok.tolist(), ref_tok.tolist())
     # the peer step inside a CUDA graph: the step number lives on the device, so replays stay in step
     sp = args()
     ph = VocabShardedLMHead(mine, a, V, peer=peer)

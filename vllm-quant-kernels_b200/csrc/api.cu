@@ -6,6 +6,7 @@
 #include <new>
 
 #include "lm_head.cuh"
+#include "peer_exchange.cuh"
 
 namespace vqk {
 
@@ -39,6 +40,14 @@ int require_sm100() {
   return g_cc_major[dev] == 10 ? VQK_OK : VQK_ERR_ARCH;
 }
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("VQK_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int device_sm_count() {
   int dev;
   if (query_device(&dev)) return 0;
@@ -65,10 +74,53 @@ struct LmHeadWs {
   float* slice_max;
   float* part_score;
   int* part_token;
+  float* list_v;  // decode-sized batches only
+  int* list_t;
+  int* row_flag;
   __half* cand;
   long long ld_cand;
   size_t total;
 };
+
+// Ticket counters of the fused sampler tail: one slot per vqk_lm_head, handed out round-robin.
+// Zero at load; the last CTA of every launch puts its slot back to zero.  In host code the array's
+// name is only a stand-in: the device address is looked up once per device.
+constexpr int kTicketSlots = 256;
+static __device__ unsigned int g_tickets[kTicketSlots];
+static unsigned int* g_tickets_ptr[64];
+static int ticket_base(unsigned int** out) {
+  int dev = 0;
+  VQK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
+  if (!g_tickets_ptr[dev]) {
+    void* ptr = nullptr;
+    VQK_CUDA(cudaGetSymbolAddress(&ptr, g_tickets));
+    g_tickets_ptr[dev] = (unsigned int*)ptr;
+  }
+  *out = g_tickets_ptr[dev];
+  return VQK_OK;
+}
+
+// Error word of the peer exchange (a wait that ran out), one per device, same address rule.
+static __device__ int g_peer_error;
+static int* g_peer_error_ptr[64];
+static int peer_error_word(int** out) {
+  int dev = 0;
+  VQK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
+  if (!g_peer_error_ptr[dev]) {
+    void* ptr = nullptr;
+    VQK_CUDA(cudaGetSymbolAddress(&ptr, g_peer_error));
+    g_peer_error_ptr[dev] = (int*)ptr;
+  }
+  *out = g_peer_error_ptr[dev];
+  return VQK_OK;
+}
+static int peer_error_flag() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
 
 static LmHeadWs carve_lm_head(void* base, int mode, long long V, long long K, long long B, int sample, int nslices) {
   Carver c(base);
@@ -80,6 +132,11 @@ static LmHeadWs carve_lm_head(void* base, int mode, long long V, long long K, lo
     w.slice_max = c.take<float>((size_t)B * nslices);
     w.part_score = c.take<float>((size_t)B * nslices);
     w.part_token = c.take<int>((size_t)B * nslices);
+    if (B <= kTailMaxBatch) {
+      w.list_v = c.take<float>((size_t)B * nslices * kListLen);
+      w.list_t = c.take<int>((size_t)B * nslices * kListM);
+    }
+    w.row_flag = c.take<int>((size_t)B);
     w.ld_cand = (V + 7) & ~7LL;
     w.cand = c.take<__half>((size_t)B * w.ld_cand);
   }
@@ -100,6 +157,8 @@ struct vqk_lm_head {
   const void* scales;
   long long V, H;
   cudaEvent_t ev_start, ev_stop;
+  int ticket_slot;
+  unsigned long long* dbg;
 };
 
 extern "C" int vqk_version(void) { return VQK_VERSION; }
@@ -126,6 +185,14 @@ extern "C" int vqk_device_error(void) {
   return (b < 0 || c < 0 || d < 0) ? -1 : (b | c | d);
 }
 
+extern "C" int vqk_device_error_clear(void) {
+  const int zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return VQK_ERR_CUDA;
+  if (umma_error_clear() || umma_mx_error_clear()) return VQK_ERR_CUDA;
+  VQK_CUDA(cudaMemcpyToSymbol(g_peer_error, &zero, sizeof(int)));
+  return VQK_OK;
+}
+
 extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, int64_t V, int64_t H,
                                   vqk_lm_head** out) {
   if (!out) return VQK_ERR_INVALID;
@@ -139,7 +206,9 @@ extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, i
   vqk_lm_head* h = new (std::nothrow) vqk_lm_head;
   if (!h) return VQK_ERR_INVALID;
   h->mode = mode; h->q = (const uint8_t*)q; h->scales = scales; h->V = V; h->H = H;
-  h->ev_start = nullptr; h->ev_stop = nullptr;
+  h->ev_start = nullptr; h->ev_stop = nullptr; h->dbg = nullptr;
+  static unsigned int next_slot = 0;
+  h->ticket_slot = (int)(__atomic_fetch_add(&next_slot, 1u, __ATOMIC_RELAXED) % kTicketSlots);
   *out = h;
   return VQK_OK;
 }
@@ -156,6 +225,12 @@ extern "C" int vqk_lm_head_set_kernel_events(vqk_lm_head* h, void* start_event, 
   return VQK_OK;
 }
 
+extern "C" int vqk_lm_head_set_debug_times(vqk_lm_head* h, void* device_buffer) {
+  if (!h) return VQK_ERR_INVALID;
+  h->dbg = (unsigned long long*)device_buffer;
+  return VQK_OK;
+}
+
 extern "C" int64_t vqk_lm_head_workspace_bytes(const vqk_lm_head* h, int64_t B, int sample) {
   if (!h || B < 0) return VQK_ERR_INVALID;
   int sms = device_sm_count();
@@ -163,17 +238,22 @@ extern "C" int64_t vqk_lm_head_workspace_bytes(const vqk_lm_head* h, int64_t B, 
   return (int64_t)carve_lm_head(nullptr, h->mode, h->V, h->H, B, sample, sms * 4).total;
 }
 
-extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, int64_t B, int64_t ldx,
-                                   const void* bias, void* logits, int64_t ld_logits, const vqk_sample_params* sp,
-                                   int64_t* tokens, float* scores, void* records, void* workspace,
-                                   int64_t workspace_bytes, void* stream) {
+struct vqk_peer;
+static int peer_table_of(const vqk_peer* p, int64_t B, PeerTable* out);
+
+// lm_head (+ sampler) of one shard; with `peer` the step is sharded: records travel over peer memory
+// and `tokens` receives the merged result.
+static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int64_t B, int64_t ldx, const void* bias,
+                                void* logits, int64_t ld_logits, const vqk_sample_params* sp, int64_t* tokens,
+                                float* scores, void* records, const vqk_peer* peer, void* workspace,
+                                int64_t workspace_bytes, void* stream) {
   if (!h || !x || B < 0 || ldx < h->H) return VQK_ERR_INVALID;
   if (x_dtype != VQK_F16 && x_dtype != VQK_BF16) return VQK_ERR_INVALID;
   if (logits && ld_logits < h->V) return VQK_ERR_INVALID;
   if (!logits && !sp) return VQK_ERR_INVALID;
   if (sp && !tokens && !records) return VQK_ERR_INVALID;
   if (sp && sp->temperature && !sp->seeds) return VQK_ERR_INVALID;
-  if (sp && tokens && (sp->vocab_total != h->V || sp->vocab_offset != 0)) return VQK_ERR_INVALID;
+  if (sp && tokens && !peer && (sp->vocab_total != h->V || sp->vocab_offset != 0)) return VQK_ERR_INVALID;
   if (sp && (sp->vocab_offset < 0 || sp->vocab_offset + h->V > sp->vocab_total || sp->vocab_total > 0x7fffffffLL))
     return VQK_ERR_INVALID;
   if (B > 65535) return VQK_ERR_TOO_LARGE;
@@ -203,6 +283,11 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   else maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
 
+  PeerTable pt{};
+  if (peer) {
+    rc = peer_table_of(peer, B, &pt);
+    if (rc) return rc;
+  }
   LmHeadWs ws = carve_lm_head(workspace, mode, h->V, h->H, B, sp != nullptr, nslices);
   const bool needs_ws = ws.total > 0 && (mode != VQK_MODE_W8A16 || sp);
   if (needs_ws && (!workspace || (size_t)workspace_bytes < ws.total)) return VQK_ERR_WORKSPACE;
@@ -214,6 +299,19 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   }
   SampleDev sd{};
   if (sp) sd = to_dev(sp);
+  // Decode-sized batches: the lm_head kernel's last CTA resolves the rows itself (tail.cuh); the
+  // full-row kernel behind it only picks up rows the tail flagged.
+  static const int tail_mode = [] {
+    const char* e = getenv("VQK_TAIL_MODE");  // A/B runs: 0 = no tail, 2 = tail sends every row to the full-row kernel
+    const int v = e ? atoi(e) : 1;
+    return v >= 0 && v <= 2 ? v : 1;
+  }();
+  const bool fuse_tail = tail_mode && sp && B <= kTailMaxBatch && B <= maxcols && nslices <= 1024;
+  unsigned int* tickets = nullptr;
+  if (fuse_tail) {
+    rc = ticket_base(&tickets);
+    if (rc) return rc;
+  }
 
   if (h->ev_start) VQK_CUDA(cudaEventRecord(h->ev_start, st));
   for (long long b0 = 0; b0 < B; b0 += maxcols) {
@@ -232,6 +330,8 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
       if (mode == VQK_MODE_W8A8) p.xscale = ws.xs;
       else if (mode != VQK_MODE_FP8) p.xscale = ws.xs + (size_t)b0 * (h->H / GROUP);
     }
+    p.dbg = h->dbg;
+    p.pdl = (mode != VQK_MODE_W8A16 && b0 == 0 && pdl_enabled()) ? 1 : 0;
     p.bias = (const __half*)bias;
     p.logits = logits ? (__half*)logits + (size_t)b0 * ld_logits : nullptr;
     p.ld_logits = ld_logits;
@@ -251,6 +351,16 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
         p.cand_logits = ws.cand + (size_t)b0 * ws.ld_cand;
         p.ld_cand = ws.ld_cand;
       }
+      if (fuse_tail) {
+        p.fuse_tail = tail_mode;
+        p.list_v = ws.list_v;
+        p.list_t = ws.list_t;
+        p.ticket = tickets + h->ticket_slot;
+        p.row_flag = ws.row_flag;
+        p.tokens = (long long*)tokens; p.scores = scores; p.records = (uint8_t*)records;
+        p.single_shard = (tokens && !peer) ? 1 : 0;
+        p.peer = pt;
+      }
     }
     rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
                    : launch_lm_head_stream(mode, p, sms, st);
@@ -264,8 +374,18 @@ extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, i
   s.V = (int)h->V; s.B = (int)B; s.sp = sd;
   s.slice_max = ws.slice_max; s.part_score = ws.part_score; s.part_token = ws.part_token; s.nslices = nslices;
   s.records = (uint8_t*)records; s.tokens = (long long*)tokens; s.scores = scores;
-  s.single_shard = tokens ? 1 : 0;
+  s.single_shard = (tokens && !peer) ? 1 : 0;
+  s.row_flag = fuse_tail ? ws.row_flag : nullptr;
+  s.peer = pt;
   return launch_select(s, st);
+}
+
+extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, int64_t B, int64_t ldx,
+                                   const void* bias, void* logits, int64_t ld_logits, const vqk_sample_params* sp,
+                                   int64_t* tokens, float* scores, void* records, void* workspace,
+                                   int64_t workspace_bytes, void* stream) {
+  return lm_head_forward_impl(h, x, x_dtype, B, ldx, bias, logits, ld_logits, sp, tokens, scores, records, nullptr,
+                              workspace, workspace_bytes, stream);
 }
 
 // ---- stand-alone sampler ----------------------------------------------------------------------
@@ -436,25 +556,41 @@ extern "C" int vqk_comm_destroy(vqk_comm* c) {
 struct vqk_peer {
   int rank, nranks;
   long long max_rows;
-  void* local;       // own landing buffer | flag words | step counters
-  void* mapped[8];   // peers' buffers opened through CUDA IPC (null for the own rank)
-  PeerTable pt;
+  void* local;       // own landing buffer | step counters
+  void* mapped[8];   // peers' buffers opened through CUDA IPC (null for the own rank and for caller-owned pointers)
+  unsigned long long* land[8];
+  unsigned int wait_polls;
   bool connected;
 };
 namespace {
-size_t peer_data_bytes(int G, long long rows) { return (size_t)2 * G * rows * VQK_RECORD_BYTES; }
-size_t peer_flag_bytes(int G, long long rows) { return (((size_t)G * rows * sizeof(unsigned int)) + 255) & ~(size_t)255; }
+size_t peer_data_bytes(int G, long long rows) { return (size_t)2 * G * rows * kWireWords * sizeof(unsigned long long); }
+constexpr unsigned int kPeerDefaultPolls = 1u << 22;  // about a second of polling, then the row reports -1
 }  // namespace
+
+static int peer_table_of(const vqk_peer* p, int64_t B, PeerTable* out) {
+  if (!p->connected) return VQK_ERR_INVALID;
+  if (B > p->max_rows) return VQK_ERR_TOO_LARGE;
+  PeerTable pt{};
+  for (int g = 0; g < p->nranks; ++g) pt.land[g] = p->land[g];
+  pt.steps = (unsigned int*)((uint8_t*)p->local + peer_data_bytes(p->nranks, p->max_rows));
+  int rc = peer_error_word(&pt.error);
+  if (rc) return rc;
+  pt.wait_polls = p->wait_polls;
+  pt.rank = p->rank; pt.G = p->nranks; pt.max_rows = (int)p->max_rows;
+  *out = pt;
+  return VQK_OK;
+}
 
 extern "C" int vqk_peer_create(int rank, int nranks, int64_t max_rows, vqk_peer** out, void* handle_out_host) {
   if (!out || !handle_out_host || nranks <= 0 || nranks > VQK_PEER_MAX_RANKS || rank < 0 || rank >= nranks ||
       max_rows <= 0 || max_rows > 65535)
     return VQK_ERR_INVALID;
   static_assert(sizeof(cudaIpcMemHandle_t) == VQK_PEER_HANDLE_BYTES, "IPC handle size");
+  static_assert(kWireWords * sizeof(unsigned long long) == VQK_RECORD_BYTES, "a record's wire form fills a record slot");
   *out = nullptr;
   int rc = require_sm100();
   if (rc) return rc;
-  const size_t bytes = peer_data_bytes(nranks, max_rows) + peer_flag_bytes(nranks, max_rows) + (size_t)max_rows * sizeof(unsigned int);
+  const size_t bytes = peer_data_bytes(nranks, max_rows) + (size_t)max_rows * sizeof(unsigned int);
   void* base = nullptr;
   VQK_CUDA(cudaMalloc(&base, bytes));
   cudaError_t e = cudaMemset(base, 0, bytes);
@@ -469,6 +605,7 @@ extern "C" int vqk_peer_create(int rank, int nranks, int64_t max_rows, vqk_peer*
   vqk_peer* p = new (std::nothrow) vqk_peer();
   if (!p) { cudaFree(base); return VQK_ERR_INVALID; }
   p->rank = rank; p->nranks = nranks; p->max_rows = max_rows; p->local = base; p->connected = false;
+  p->wait_polls = kPeerDefaultPolls;
   memcpy(handle_out_host, &h, sizeof(h));
   *out = p;
   return VQK_OK;
@@ -476,7 +613,6 @@ extern "C" int vqk_peer_create(int rank, int nranks, int64_t max_rows, vqk_peer*
 
 extern "C" int vqk_peer_connect(vqk_peer* p, const void* all_handles_host) {
   if (!p || !all_handles_host || p->connected) return VQK_ERR_INVALID;
-  const size_t data = peer_data_bytes(p->nranks, p->max_rows), flags = peer_flag_bytes(p->nranks, p->max_rows);
   for (int g = 0; g < p->nranks; ++g) {
     void* base = p->local;
     if (g != p->rank) {
@@ -491,20 +627,62 @@ extern "C" int vqk_peer_connect(vqk_peer* p, const void* all_handles_host) {
       }
       p->mapped[g] = base;
     }
-    p->pt.land[g] = (uint8_t*)base;
-    p->pt.flags[g] = (unsigned int*)((uint8_t*)base + data);
+    p->land[g] = (unsigned long long*)base;
   }
-  p->pt.steps = (unsigned int*)((uint8_t*)p->local + data + flags);
   p->connected = true;
+  return VQK_OK;
+}
+
+extern "C" void* vqk_peer_local_buffer(vqk_peer* p) { return p ? p->local : nullptr; }
+
+extern "C" int vqk_peer_connect_pointers(vqk_peer* p, void* const* buffers_host) {
+  if (!p || !buffers_host || p->connected) return VQK_ERR_INVALID;
+  for (int g = 0; g < p->nranks; ++g) {
+    void* base = g == p->rank ? p->local : buffers_host[g];
+    if (!base || ((uintptr_t)base & 7)) return VQK_ERR_INVALID;
+    p->land[g] = (unsigned long long*)base;
+  }
+  p->connected = true;
+  return VQK_OK;
+}
+
+extern "C" int vqk_peer_set_wait_limit(vqk_peer* p, int64_t polls) {
+  if (!p || polls < 1 || polls > 0x7fffffffLL) return VQK_ERR_INVALID;
+  p->wait_polls = (unsigned int)polls;
   return VQK_OK;
 }
 
 extern "C" int vqk_peer_exchange_finalize(vqk_peer* p, const void* records, int64_t B, const vqk_sample_params* sp,
                                           int64_t* tokens, float* scores, void* stream) {
   if (!p || !p->connected || !records || !sp || !tokens || B < 0) return VQK_ERR_INVALID;
+  if (sp->temperature && !sp->seeds) return VQK_ERR_INVALID;
   if (B > p->max_rows) return VQK_ERR_TOO_LARGE;
-  return launch_peer_exchange((const uint8_t*)records, (int)B, p->rank, p->nranks, (int)p->max_rows, p->pt, to_dev(sp),
-                              (long long*)tokens, scores, (cudaStream_t)stream);
+  int rc = require_sm100();
+  if (rc) return rc;
+  PeerTable pt{};
+  rc = peer_table_of(p, B, &pt);
+  if (rc) return rc;
+  return launch_peer_exchange((const uint8_t*)records, (int)B, pt, to_dev(sp), (long long*)tokens, scores,
+                              (cudaStream_t)stream);
+}
+
+extern "C" int vqk_lm_head_step_sharded(vqk_lm_head* h, vqk_peer* peer, const void* x, int x_dtype, int64_t B,
+                                        int64_t ldx, const void* bias, const vqk_sample_params* sp, int64_t* tokens,
+                                        float* scores, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!peer || !sp || !tokens) return VQK_ERR_INVALID;
+  // the workspace holds the records of the rows the full-row kernel resolves, after the rest
+  const int64_t base = vqk_lm_head_workspace_bytes(h, B, 1);
+  if (base < 0) return (int)base;
+  const int64_t need = base + B * VQK_RECORD_BYTES;
+  if (!workspace || workspace_bytes < need) return VQK_ERR_WORKSPACE;
+  void* records = (uint8_t*)workspace + base;
+  return lm_head_forward_impl(h, x, x_dtype, B, ldx, bias, nullptr, 0, sp, tokens, scores, records, peer, workspace,
+                              base, stream);
+}
+
+extern "C" int64_t vqk_lm_head_step_sharded_workspace_bytes(const vqk_lm_head* h, int64_t B) {
+  const int64_t base = vqk_lm_head_workspace_bytes(h, B, 1);
+  return base < 0 ? base : base + B * VQK_RECORD_BYTES;
 }
 
 extern "C" int vqk_peer_destroy(vqk_peer* p) {

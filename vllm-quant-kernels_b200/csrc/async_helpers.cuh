@@ -15,6 +15,11 @@ static inline int read_stream_error() {
   return v;
 }
 
+static inline int clear_stream_error() {
+  const int zero = 0;
+  return cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
+
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -5,6 +5,15 @@
 
 namespace vqk {
 
+// Record exchange over peer memory (peer_exchange.cuh).  G == 0: no exchange.
+struct PeerTable {
+  unsigned long long* land[8];  // every rank's landing buffer [2][G][max_rows][kWireWords] words (own one included)
+  unsigned int* steps;          // this rank's per-row step counters [max_rows]
+  int* error;                   // device error word, set when a wait runs out
+  unsigned int wait_polls;      // bound of every wait, in polls
+  int rank, G, max_rows;
+};
+
 struct LmHeadParams {
   const uint8_t* w;    // quantized rows [V, K] bytes (MXFP4: [V, K/2])
   const void* wscale;  // fp16 [V] / fp32 [V] / E8M0 [V, K/32]
@@ -24,7 +33,33 @@ struct LmHeadParams {
   int nslices;
   __half* cand_logits; // [B, ld_cand] fp16 logits of candidate-path rows (scratch or == logits)
   long long ld_cand;
+  int pdl;             // launched as a programmatic dependent of the activation quantizer
+  unsigned long long* dbg;  // null, or [gridDim.x][16] time stamps (vqk_lm_head_set_debug_times)
+  // decode-sized batches: the last CTA to finish resolves the rows (tail.cuh)
+  int fuse_tail;
+  float* list_v;         // [B][kListLen][nslices] largest logits per slice, descending; position kListM is the witness
+  int* list_t;           // [B][kListM][nslices] their LOCAL token ids (null together with list_v: no lists)
+  unsigned int* ticket;  // device counter, zero between launches
+  int* row_flag;         // [B] written by the tail: 1 = the row still needs the full-row kernel
+  long long* tokens;     // outputs of the tail (as SelectParams)
+  float* scores;
+  uint8_t* records;
+  int single_shard;
+  PeerTable peer;        // sharded step: the tail also exchanges the row's record and merges (G > 0)
 };
+
+// time stamp i of this CTA (measurement aid; %globaltimer, nanoseconds)
+__device__ __forceinline__ void dbg_stamp(const LmHeadParams& p, int i) {
+  if (p.dbg && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.dbg[(size_t)blockIdx.x * 16 + i] = t;
+  }
+}
+
+constexpr int kListM = 4;            // entries of a slice list that can be used ...
+constexpr int kListLen = kListM + 1;  // ... plus the witness: every logit of the slice outside the list is <= it
+constexpr int kTailMaxBatch = 16;    // largest batch whose rows the lm_head kernel resolves itself
 
 // lm_head_stream.cu
 size_t stream_smem_bytes(int mode, int K, int NT);
@@ -36,10 +71,12 @@ int launch_lm_head_stream(int mode, const LmHeadParams& p, int grid, cudaStream_
 int umma_max_cols(int mode, int K);    // 256, or 0 when the mode / shape is not covered
 int launch_lm_head_umma(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
 int umma_error_flag();
+int umma_error_clear();
 // lm_head_umma_mx.cu: block-scaled tcgen05 kernel (MXFP8, MXFP4; K % 128 == 0; up to 128 columns)
 int umma_mx_max_cols(int mode, int K);
 int launch_lm_head_umma_mx(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
 int umma_mx_error_flag();
+int umma_mx_error_clear();
 
 // quantize.cu
 int quantize_act_dispatch(int mode, const void* x, int dt, long long B, long long H, long long ldx, void* xq,
@@ -61,6 +98,8 @@ struct SelectParams {
   long long* tokens;    // final answers when single shard (may be null)
   float* scores;
   int single_shard;     // 1: also resolve candidate rows to a final token here
+  const int* row_flag;  // null, or [B]: rows whose flag is 0 were resolved by the lm_head kernel's tail
+  PeerTable peer;       // G > 0: rank 0 of the row's cluster also exchanges the record and merges (sharded step)
 };
 
 // first pass over materialised logits: per-slice maxima / Gumbel winners (slices of 256 columns)
@@ -73,15 +112,8 @@ int launch_select(const SelectParams& p, cudaStream_t st);
 // merge gathered records
 int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, long long* tokens, float* scores,
                     cudaStream_t st);
-// record exchange over peer memory fused with the merge (sampler.cu: k_peer_exchange)
-struct PeerTable {
-  uint8_t* land[8];        // every rank's landing buffer [2][G][max_rows][VQK_RECORD_BYTES] (own one included)
-  unsigned int* flags[8];  // every rank's flag words [G][max_rows]
-  unsigned int* steps;     // this rank's step counters [max_rows]
-};
-int launch_peer_exchange(const uint8_t* mine, int B, int rank, int G, int max_rows, const PeerTable& pt,
-                         const SampleDev& sp, long long* tokens, float* scores, cudaStream_t st);
-int peer_error_flag();
+int launch_peer_exchange(const uint8_t* mine, int B, const PeerTable& pt, const SampleDev& sp, long long* tokens,
+                         float* scores, cudaStream_t st);
 // sampler on materialised logits with its scratch in a static device array (no allocation)
 int sample_static(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, long long* tokens,
                   float* scores, cudaStream_t st);

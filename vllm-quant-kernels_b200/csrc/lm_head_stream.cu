@@ -13,6 +13,7 @@
 
 #include "lm_head.cuh"
 #include "mma_helpers.cuh"
+#include "tail.cuh"
 
 namespace vqk {
 
@@ -56,10 +57,16 @@ __host__ __device__ inline size_t stream_sx_bytes(int mode, int K, int NT) {
   return (mode == VQK_MODE_MXFP8 || mode == VQK_MODE_MXFP4) ? (size_t)(K / GROUP) * NT * 8 * sizeof(float) : 0;
 }
 __host__ __device__ inline size_t stream_red_bytes(int NT) { return (size_t)16 * NT * 128 * 4; }
-size_t stream_smem_bytes(int mode, int K, int NT) {
-  return stream_xfrag_bytes(mode, K, NT) + stream_sx_bytes(mode, K, NT) + stream_red_bytes(NT) +
-         (size_t)NT * 8 * sizeof(RowMeta);
+// per warp group and batch column: the kListLen largest logits of the group's slice (sampler, top-k rows)
+__host__ __device__ inline size_t stream_tlist_bytes(int NT) { return (size_t)kGroups * NT * 8 * kListLen * sizeof(Cand); }
+// (the sampler tail reuses the buffer once the main loop is over: one warp's scratch per batch row)
+__host__ __device__ inline size_t stream_smem_total(int mode, int K, int NT, int B) {
+  const size_t main_loop = stream_xfrag_bytes(mode, K, NT) + stream_sx_bytes(mode, K, NT) + stream_red_bytes(NT) +
+                           (size_t)NT * 8 * sizeof(RowMeta) + stream_tlist_bytes(NT);
+  const size_t tail = tail_smem_bytes(B < NT * 8 ? B : NT * 8);
+  return main_loop > tail ? main_loop : tail;
 }
+size_t stream_smem_bytes(int mode, int K, int NT) { return stream_smem_total(mode, K, NT, NT * 8); }
 
 template <int MODE, int NT, int U, bool EVEN>
 __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadParams p) {
@@ -70,7 +77,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   float* sxf = reinterpret_cast<float*>(smem + stream_xfrag_bytes(MODE, p.K, NT));
   acc_t* red = reinterpret_cast<acc_t*>(smem + stream_xfrag_bytes(MODE, p.K, NT) + stream_sx_bytes(MODE, p.K, NT));
   RowMeta* meta = reinterpret_cast<RowMeta*>(reinterpret_cast<uint8_t*>(red) + stream_red_bytes(NT));
+  Cand* slist = reinterpret_cast<Cand*>(meta + NT * 8) + (size_t)(threadIdx.x >> 7) * NT * 8 * kListLen;  // this group's lists [column][entry]
 
+  dbg_stamp(p, 0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = warp >> 2, wq = warp & 3;
   const int g = lane >> 2, t = lane & 3;
@@ -81,10 +90,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   // ---- per-thread sampler state: epilogue thread e of a group owns (row e%16, col e/16) ----
   const int e = tid & 127;
   const int er = e & 15, ec = e >> 4;
-  float smax[NT], bs[NT];
+  // rows without top-k / top-p: the running Gumbel (or greedy) winner of this thread's rows
+  float bs[NT];
   int bt[NT];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) { smax[nt] = -INFINITY; bs[nt] = -INFINITY; bt[nt] = 0x7fffffff; }
+  for (int nt = 0; nt < NT; ++nt) { bs[nt] = -INFINITY; bt[nt] = 0x7fffffff; }
+  if (p.do_sample)
+    for (int i = threadIdx.x & 127; i < NT * 8 * kListLen; i += 128) slist[i] = Cand{-INFINITY, 0x7fffffff};
 
   const int ntiles = (V + 15) / 16;
   const size_t rowbytes = (MODE == VQK_MODE_MXFP4) ? (size_t)K / 2 : (size_t)K;
@@ -242,6 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   if (have) issue(buf0, tile, 0);
 
   // ---- activations -> B fragments in shared memory, while the first weight loads are in flight ----
+  if constexpr (MODE != VQK_MODE_W8A16) pdl_wait();  // the quantized activations come from the kernel before
   if constexpr (MODE == VQK_MODE_W8A16) {
     // one item = the four fragments (i = 0..3) a lane needs for a 64-wide k-step: the sixteen
     // consecutive activations k .. k + 15 of batch row b, fetched with two 16-byte loads when the
@@ -350,75 +363,101 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
 
     // ---- epilogue: thread e -> (vocab row row0 + er, batch column nt*8 + ec) ------------
     const int row = row0 + er;
-    if (row < V) {
-      float rs = 1.f;
+    const bool row_ok = row < V;
+    float rs = 1.f, bias = 0.f;
+    if (row_ok) {
       if constexpr (MODE == VQK_MODE_W8A16 || MODE == VQK_MODE_FP8)
         rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[row]);
       if constexpr (MODE == VQK_MODE_W8A8) rs = reinterpret_cast<const float*>(p.wscale)[row];
-      float bias = p.bias ? __half2float(p.bias[row]) : 0.f;
+      if (p.bias) bias = __half2float(p.bias[row]);
+    }
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int b = nt * 8 + ec;
-        if (b < B) {
-          acc_t s = gred[0 * NT * 128 + nt * 128 + e] + gred[1 * NT * 128 + nt * 128 + e] +
-                    gred[2 * NT * 128 + nt * 128 + e] + gred[3 * NT * 128 + nt * 128 + e];
-          float v;
-          if constexpr (MODE == VQK_MODE_W8A8) v = ((float)s * rs) * xs_w8a8;   // _kernels.py:471, left to right
-          else if constexpr (MX) v = s;
-          else v = s * rs;
-          __half h = __float2half_rn(v);
-          if (p.bias) h = __float2half_rn(__half2float(h) + bias);
-          if (p.logits) p.logits[(long long)b * p.ld_logits + row] = h;
-          if (p.do_sample) {
-            const RowMeta m = meta[b];
-            const float l = __half2float(h);
-            if (m.flags & ROW_CAND) {
-              p.cand_logits[(long long)b * p.ld_cand + row] = h;
-              smax[nt] = fmaxf(smax[nt], l);
-            } else {
-              float sc = l;
-              const int tok = row;  // local id; offset added by the consumer
-              if (!(m.flags & ROW_GREEDY)) {
-                sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(row + p.sp.vocab_offset));
-                if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
-              }
-              if (better(sc, tok, bs[nt], bt[nt])) { bs[nt] = sc; bt[nt] = tok; }
+    for (int nt = 0; nt < NT; ++nt) {
+      const int b = nt * 8 + ec;
+      bool pass = false;  // a top-k column's logit that beats the last entry of the slice's list
+      float l = 0.f;
+      if (row_ok && b < B) {
+        acc_t s = gred[0 * NT * 128 + nt * 128 + e] + gred[1 * NT * 128 + nt * 128 + e] +
+                  gred[2 * NT * 128 + nt * 128 + e] + gred[3 * NT * 128 + nt * 128 + e];
+        float v;
+        if constexpr (MODE == VQK_MODE_W8A8) v = ((float)s * rs) * xs_w8a8;   // _kernels.py:471, left to right
+        else if constexpr (MX) v = s;
+        else v = s * rs;
+        __half h = __float2half_rn(v);
+        if (p.bias) h = __float2half_rn(__half2float(h) + bias);
+        if (p.logits) p.logits[(long long)b * p.ld_logits + row] = h;
+        if (p.do_sample) {
+          const RowMeta m = meta[b];
+          l = __half2float(h);
+          if (m.flags & ROW_CAND) {
+            p.cand_logits[(long long)b * p.ld_cand + row] = h;
+            pass = l > slist[b * kListLen + kListM].v;
+          } else {
+            float sc = l;
+            const int tok = row;  // local id; offset added by the consumer
+            if (!(m.flags & ROW_GREEDY)) {
+              sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(row + p.sp.vocab_offset));
+              if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
             }
+            if (better(sc, tok, bs[nt], bt[nt])) { bs[nt] = sc; bt[nt] = tok; }
           }
+        }
+      }
+      if (p.do_sample) {
+        // The slice's kListLen largest logits per column live in shared memory.  Once the list has
+        // warmed up hardly any logit beats its last entry, so this is one vote per tile; the few
+        // that do go in one after the other (a warp holds two columns, sixteen rows each).
+        unsigned mask = __ballot_sync(0xffffffffu, pass);
+        while (mask) {
+          const int src = __ffs(mask) - 1;
+          mask &= mask - 1;
+          if (lane == src) list_insert(slist + b * kListLen, kListLen, l, row);
+          __syncwarp();
         }
       }
     }
     asm volatile("bar.sync %0, 128;" ::"r"(group + 1));
   }
 
+  dbg_stamp(p, 1);
   // ---- per-slice sampler results: reduce over the 16 row-threads of each column ----------
   if (p.do_sample) {
     const int slice = blockIdx.x * kGroups + group;
+    __syncwarp();
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      float m = smax[nt], s = bs[nt];
+      float s = bs[nt];
       int tk = bt[nt];
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) {
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         float s2 = __shfl_xor_sync(0xffffffffu, s, o);
         int t2 = __shfl_xor_sync(0xffffffffu, tk, o);
         if (better(s2, t2, s, tk)) { s = s2; tk = t2; }
       }
       const int b = nt * 8 + ec;
-      if (er == 0 && b < B) {
-        p.slice_max[(long long)b * p.nslices + slice] = m;
-        p.part_score[(long long)b * p.nslices + slice] = s;
-        p.part_token[(long long)b * p.nslices + slice] = tk;
+      if (b < B) {
+        const long long o = (long long)b * p.nslices + slice;
+        if (p.list_v && er < kListLen) {  // row-thread i of the column writes list entry i
+          const Cand mine = slist[b * kListLen + er];
+          p.list_v[((long long)b * kListLen + er) * p.nslices + slice] = mine.v;
+          if (er < kListM) p.list_t[((long long)b * kListM + er) * p.nslices + slice] = mine.t;
+        }
+        if (er == 0) {
+          p.slice_max[o] = slist[b * kListLen].v;
+          p.part_score[o] = s;
+          p.part_token[o] = tk;
+        }
       }
     }
+    dbg_stamp(p, 2);
+    if (p.fuse_tail) lm_head_tail(p, smem, stream_smem_total(MODE, p.K, NT, B));
   }
 }
 
 // ---- host launch -------------------------------------------------------------------------
 template <int MODE, int NT, int U, bool EVEN>
 static int launch_stream(const LmHeadParams& p, int grid, cudaStream_t st) {
-  size_t smem = stream_smem_bytes(MODE, p.K, NT);
+  size_t smem = stream_smem_total(MODE, p.K, NT, p.B);
   static size_t configured[64] = {};  // per device: largest opt-in so far for this instantiation
   int dev = 0;
   VQK_CUDA(cudaGetDevice(&dev));
@@ -428,8 +467,7 @@ static int launch_stream(const LmHeadParams& p, int grid, cudaStream_t st) {
                                   (int)smem));
     configured[dev] = smem;
   }
-  k_lm_head_stream<MODE, NT, U, EVEN><<<grid, kThreads, smem, st>>>(p);
-  VQK_LAUNCH_CHECK();
+  VQK_CUDA(launch_kernel(k_lm_head_stream<MODE, NT, U, EVEN>, dim3(grid), dim3(kThreads), smem, st, p.pdl != 0, p));
   return VQK_OK;
 }
 

@@ -39,7 +39,7 @@ __host__ __device__ inline Geometry geometry(int bn, int ni) {
   Geometry g;
   g.stage_bytes = BM * BK + bn * BK;
   const size_t fixed = 1024 /* alignment slack */ + 1024 /* barriers */ + (size_t)bn * sizeof(RowMeta) +
-                       (size_t)12 * bn * sizeof(int) /* sampler state */;
+                       epi_state_bytes(bn) /* sampler state */;
   const size_t limit = 227 * 1024;
   int s = (int)((limit - fixed) / g.stage_bytes) / ni;
   g.stages_per_lane = s > kMaxStages ? kMaxStages : s;
@@ -102,6 +102,7 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
   if (warp < NI) {
     // ================================ TMA producers =====================================
     if (lane == 0) {
+      pdl_wait();  // the quantized activations come from the kernel before
       const int l = warp;
       uint64_t* full = lane_bars + l * kPerLane;
       uint64_t* empty = full + kMaxStages;
@@ -162,7 +163,9 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
       mbar_drain(&drained[l], 0);
     }
   } else {
-    umma_epilogue<INT8 ? 1 : 0, BN, NI>(p, warp, lane, tmem_base, tfull, tempty, abort_flag, meta, sstate, ntiles);
+    pdl_wait();  // W8A8: the activation scale comes from the kernel before
+    umma_epilogue<INT8 ? 1 : 0, BN, NI>(p, warp, lane, tmem_base, tfull, tempty, abort_flag, meta, sstate, sched_interleaved(V),
+                                        reinterpret_cast<Cand*>(sstate + (size_t)12 * BN), nullptr);
   }
 
   tc_fence_before();
@@ -171,6 +174,8 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
     tc_fence_after();
     tmem_dealloc(tmem_base, TCOLS);
   }
+  // decode-sized batches: the last CTA of the grid resolves the rows; the stage ring is free by now
+  if (p.fuse_tail) lm_head_tail(p, smem, (size_t)NI * S * geo.stage_bytes);
 }
 
 
@@ -219,8 +224,7 @@ static int launch_lanes(const LmHeadParams& p, const CUtensorMap& a, const CUten
     configured[dev] = true;
   }
   // every CTA of the grid runs (those without a tile still write their empty slice records)
-  k_lm_head_umma<MODE, BN, NI><<<grid, umma_threads(NI), geo.total, st>>>(p, a, b);
-  VQK_LAUNCH_CHECK();
+  VQK_CUDA(launch_kernel(k_lm_head_umma<MODE, BN, NI>, dim3(grid), dim3(umma_threads(NI)), geo.total, st, p.pdl != 0, p, a, b));
   return VQK_OK;
 }
 // three pipelines for narrow batch tiles (issue-bound), two at 64, one from 128 columns on (the
@@ -275,5 +279,6 @@ int launch_lm_head_umma(int mode, const LmHeadParams& p, int grid, cudaStream_t 
 }
 
 int umma_error_flag() { return read_stream_error(); }
+int umma_error_clear() { return clear_stream_error(); }
 
 }  // namespace vqk

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(256) k_quant_rows(const T* __restrict__ w, lon
 template <typename T, bool FP4>
 __global__ void __launch_bounds__(256) k_quant_mx(const T* __restrict__ x, long long ldx, long long R, int H,
                                                   uint8_t* __restrict__ q, uint8_t* __restrict__ scales) {
+  pdl_launch_dependents();  // an lm_head kernel behind this one may start its set-up now
   const int lane = threadIdx.x & 31;
   const int ngroups = H / GROUP;
   long long gid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -100,6 +101,7 @@ __global__ void k_act_to_f16(const T* __restrict__ x, long long ldx, int H, __ha
 // likewise; both widen to fp32 exactly first, so one rounding either way.
 template <typename T>
 __global__ void k_act_fp8(const T* __restrict__ x, long long ldx, int H, uint8_t* __restrict__ out) {
+  pdl_launch_dependents();
   long long row = blockIdx.y;
   for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < H; k += gridDim.x * blockDim.x)
     out[row * H + k] = f32_to_e4m3_nosat(ld_f32(x + row * ldx, k));
@@ -120,12 +122,39 @@ __global__ void __launch_bounds__(256) k_act_absmax(const T* __restrict__ x, lon
 
 template <typename T>
 __global__ void k_act_int8(const T* __restrict__ x, long long ldx, int H, int8_t* __restrict__ out, float* xs) {
+  pdl_launch_dependents();
   long long row = blockIdx.y;
   float s = fmaxf(xs[1] / 127.0f, 1e-12f);
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) xs[0] = s;
   for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < H; k += gridDim.x * blockDim.x) {
     float v = rintf(ld_f32(x + row * ldx, k) / s);
     out[row * H + k] = (int8_t)(int)fminf(fmaxf(v, -127.0f), 127.0f);
+  }
+}
+
+// Decode-sized batches: absmax and quantisation by ONE block (no memset, no second launch); the
+// same arithmetic as the pair above.
+constexpr long long kActInt8OneBlock = 131072;  // elements (B * H) the single block takes
+template <typename T>
+__global__ void __launch_bounds__(1024) k_act_int8_one(const T* __restrict__ x, long long ldx, int B, int H,
+                                                       int8_t* __restrict__ out, float* xs) {
+  pdl_launch_dependents();
+  __shared__ float red[32];
+  __shared__ float s_scale;
+  const long long n = (long long)B * H;
+  float m = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, fabsf(ld_f32(x + (i / H) * ldx, i % H)));
+  m = block_max(m, red);
+  if (threadIdx.x == 0) {
+    s_scale = fmaxf(m / 127.0f, 1e-12f);
+    xs[0] = s_scale;
+    xs[1] = m;
+  }
+  __syncthreads();
+  const float s = s_scale;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = rintf(ld_f32(x + (i / H) * ldx, i % H) / s);
+    out[i] = (int8_t)(int)fminf(fmaxf(v, -127.0f), 127.0f);
   }
 }
 
@@ -165,6 +194,10 @@ static int quantize_act_t(int mode, const T* x, long long B, long long H, long l
     case VQK_MODE_FP8: k_act_fp8<T><<<grid, 256, 0, st>>>(x, ldx, (int)H, (uint8_t*)xq); break;
     case VQK_MODE_W8A8:
       if (!xs) return VQK_ERR_INVALID;
+      if (B * H <= kActInt8OneBlock) {
+        k_act_int8_one<T><<<1, 1024, 0, st>>>(x, ldx, (int)B, (int)H, (int8_t*)xq, (float*)xs);
+        break;
+      }
       VQK_CUDA(cudaMemsetAsync(xs, 0, 2 * sizeof(float), st));
       k_act_absmax<T><<<grid, 256, 0, st>>>(x, ldx, (int)H, (float*)xs);
       k_act_int8<T><<<grid, 256, 0, st>>>(x, ldx, (int)H, (int8_t*)xq, (float*)xs);

@@ -12,6 +12,7 @@
 #include <cooperative_groups.h>
 
 #include "lm_head.cuh"
+#include "tail.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -348,6 +349,19 @@ __device__ float smem_kth_largest(const float* v, int n, int k, unsigned int* hi
   return key_f32(prefix);
 }
 
+// Sharded step: the record k_select just wrote for row b travels to every rank and the shards are
+// merged, by the first warp of the row's CTA (peer_exchange.cuh).  `buf` is block shared memory of
+// at least kTailWarpBytes.
+__device__ void select_exchange_row(const SelectParams& p, int b, const RowMeta& m, uint8_t* buf) {
+  __syncthreads();  // the record of this row is complete (written by this block)
+  if (threadIdx.x >= 32) return;
+  const uint8_t* rec = p.records + (size_t)b * VQK_RECORD_BYTES;
+  const RecordHeader h = *reinterpret_cast<const RecordHeader*>(rec);
+  const Cand* cd = reinterpret_cast<const Cand*>(rec + sizeof(RecordHeader));
+  tail_exchange_row(p.peer, m, b, h.score, h.token, h.n, h.flags, [&](int i) { return cd[i]; }, buf,
+                    (int)threadIdx.x, p.tokens, p.scores);
+}
+
 // ---- pass 2: one cluster per row -----------------------------------------------------------------
 // Two cluster barriers per row.  Every CTA first puts its share of the row in flight (16-byte
 // loads into registers), then the cluster rank-counts the slice maxima for tau while those loads
@@ -365,6 +379,8 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   const int crank = (int)cluster.block_rank();
   const int csize = (int)cluster.num_blocks();  // 1, 2, 4 or 8: chosen by the launcher from the row length
   const int b = blockIdx.y, tid = threadIdx.x;
+  // rows the lm_head kernel's own tail already resolved (uniform over the cluster: no barrier is reached)
+  if (p.row_flag && p.row_flag[b] == 0) return;
   const RowMeta m = decode_row(p.sp, b);
   const T* row = reinterpret_cast<const T*>(p.logits) + (long long)b * p.ld;
 
@@ -380,6 +396,8 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   __shared__ int s_count;
   __shared__ int s_nrec;
   __shared__ FullRowScratch s_full;
+  __shared__ __align__(16) uint8_t s_xbuf[kTailWarpBytes];  // sharded step: scratch of the record exchange
+  const bool exchange = p.peer.G > 0;
 
   if (!(m.flags & ROW_CAND)) {
     // row already reduced to per-slice winners: merge them (rank 0 only, no cluster traffic)
@@ -397,6 +415,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       if (p.tokens) p.tokens[b] = tok;
       if (p.scores) p.scores[b] = best.s;
     }
+    if (exchange) select_exchange_row(p, b, m, s_xbuf);
     return;
   }
 
@@ -415,6 +434,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_NEEDS_ROW);
       if (p.tokens) p.tokens[b] = -1;
     }
+    if (exchange) select_exchange_row(p, b, m, s_xbuf);
     return;
   }
 
@@ -500,6 +520,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_OVERFLOW);
       if (p.tokens) p.tokens[b] = -1;
     }
+    if (exchange) select_exchange_row(p, b, m, s_xbuf);
     return;
   }
 
@@ -534,6 +555,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       if (p.scores) p.scores[b] = w.s;
     }
   }
+  if (exchange) select_exchange_row(p, b, m, s_xbuf);
 }
 
 // ---- merge of gathered shard records -----------------------------------------------------------
@@ -596,61 +618,19 @@ __global__ void __launch_bounds__(256) k_finalize(const uint8_t* __restrict__ re
   finalize_row(records, (size_t)B * VQK_RECORD_BYTES, G, blockIdx.x, sp, tokens, scores);
 }
 
-// ---- record exchange over peer memory + merge, one kernel ------------------------------------------
-// Every rank owns a landing buffer [2 parities][G ranks][max_rows] records, a flag word per
-// (rank, row) and a step counter per row.  The CTA of row b copies its rank's record into slot
-// [parity][rank][b] of EVERY rank's landing buffer (plain stores through NVLink peer mappings),
-// fences, publishes the row's step number in the matching flag word of every rank, then waits
-// (bounded) until the G flag words of its own buffer carry this step and merges the G records.
-// The step number lives in device memory, so a CUDA-graph replay advances it like a fresh
-// launch.  Two parities are enough: a rank can enter step t + 2 only after it has seen every
-// peer's flag of step t + 1, which a peer raises after it has finished reading step t.
-static __device__ int g_peer_error = 0;
-constexpr unsigned int kPeerSpinLimit = 1u << 23;  // a few seconds of polling, then the row reports -1
-
-__global__ void __launch_bounds__(256) k_peer_exchange(const uint8_t* __restrict__ mine, int B, int rank, int G,
-                                                       int max_rows, PeerTable pt, SampleDev sp, long long* tokens,
-                                                       float* scores) {
-  const int b = blockIdx.x, tid = threadIdx.x;
-  __shared__ unsigned int s_step;
-  __shared__ int s_late;
-  if (tid == 0) {
-    unsigned int* steps = pt.steps;
-    s_step = steps[b] + 1u;
-    steps[b] = s_step;
-    s_late = 0;
-  }
-  __syncthreads();
-  const unsigned int step = s_step;
-  const size_t slot = (((size_t)(step & 1u) * G + rank) * max_rows + b) * VQK_RECORD_BYTES;
-  const uint4* src = reinterpret_cast<const uint4*>(mine + (size_t)b * VQK_RECORD_BYTES);
-  for (int i = tid; i < G * (VQK_RECORD_BYTES / 16); i += blockDim.x) {
-    const int g = i / (VQK_RECORD_BYTES / 16), c = i % (VQK_RECORD_BYTES / 16);
-    reinterpret_cast<uint4*>(pt.land[g] + slot)[c] = src[c];
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (tid < G) {
-    unsigned int* f = pt.flags[tid] + (size_t)rank * max_rows + b;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
-    // wait for rank `tid`'s record of this step in the local buffer
-    const unsigned int* w = pt.flags[rank] + (size_t)tid * max_rows + b;
-    bool ok = false;
-    for (unsigned int it = 0; it < kPeerSpinLimit; ++it) {
-      unsigned int v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
-      if ((int)(v - step) >= 0) { ok = true; break; }
-      __nanosleep(it < 4096 ? 40 : 400);
-    }
-    if (!ok) { s_late = 1; atomicExch(&g_peer_error, 1); }
-  }
-  __syncthreads();
-  if (s_late) {
-    if (tid == 0) { tokens[b] = -1; if (scores) scores[b] = -INFINITY; }
-    return;
-  }
-  const uint8_t* landed = pt.land[rank] + (size_t)(step & 1u) * G * max_rows * VQK_RECORD_BYTES;
-  finalize_row(landed, (size_t)max_rows * VQK_RECORD_BYTES, G, b, sp, tokens, scores);
+// ---- record exchange over peer memory + merge as a kernel of its own ---------------------------------
+// One warp per row: the record the caller computed earlier (vqk_lm_head_forward / vqk_sample with
+// `records`) is sent to every rank and the shards are merged (peer_exchange.cuh).
+__global__ void __launch_bounds__(32) k_peer_exchange(const uint8_t* __restrict__ mine, PeerTable pt, SampleDev sp,
+                                                      long long* tokens, float* scores) {
+  __shared__ __align__(16) uint8_t s_xbuf[kTailWarpBytes];
+  const int b = blockIdx.x;
+  const RowMeta m = decode_row(sp, b);
+  const uint8_t* rec = mine + (size_t)b * VQK_RECORD_BYTES;
+  const RecordHeader h = *reinterpret_cast<const RecordHeader*>(rec);
+  const Cand* cd = reinterpret_cast<const Cand*>(rec + sizeof(RecordHeader));
+  tail_exchange_row(pt, m, b, h.score, h.token, h.n, h.flags, [&](int i) { return cd[i]; }, s_xbuf, (int)threadIdx.x,
+                    tokens, scores);
 }
 
 template <typename T>
@@ -732,17 +712,12 @@ int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, l
   return VQK_OK;
 }
 
-int launch_peer_exchange(const uint8_t* mine, int B, int rank, int G, int max_rows, const PeerTable& pt,
-                         const SampleDev& sp, long long* tokens, float* scores, cudaStream_t st) {
+int launch_peer_exchange(const uint8_t* mine, int B, const PeerTable& pt, const SampleDev& sp, long long* tokens,
+                         float* scores, cudaStream_t st) {
   if (B == 0) return VQK_OK;
-  k_peer_exchange<<<(unsigned)B, 256, 0, st>>>(mine, B, rank, G, max_rows, pt, sp, tokens, scores);
+  k_peer_exchange<<<(unsigned)B, 32, 0, st>>>(mine, pt, sp, tokens, scores);
   VQK_LAUNCH_CHECK();
   return VQK_OK;
-}
-int peer_error_flag() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
 }
 
 int launch_topk_threshold(const void* logits, int dtype, long long ld, int B, int V, const int32_t* top_k, float* thr,

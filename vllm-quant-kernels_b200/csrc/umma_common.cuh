@@ -5,6 +5,7 @@
 
 #include "async_helpers.cuh"
 #include "lm_head.cuh"
+#include "tail.cuh"
 
 namespace vqk {
 namespace umma {
@@ -12,6 +13,10 @@ namespace umma {
 constexpr int BM = 128;        // vocab rows per tile = TMEM lanes
 constexpr int BK = 128;        // bytes of K per stage in shared memory: one 128-byte swizzle row
 constexpr int kMaxStages = 8;
+// sampler state of the four epilogue warps in shared memory: [4][3][BN] ints (slice maximum, best Gumbel
+// score, its token) and, for decode-sized batches, [4][kTailMaxBatch][kListLen] largest logits per column
+constexpr size_t kEpiListBytes = (size_t)4 * kTailMaxBatch * kListLen * sizeof(Cand);
+__host__ __device__ inline size_t epi_state_bytes(int bn) { return (size_t)12 * bn * sizeof(int) + kEpiListBytes; }
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -89,6 +94,57 @@ __host__ __device__ inline uint32_t instr_desc(bool int8, int bn) {
   return d;
 }
 
+// Which vocab rows a CTA works on, as a sequence of tiles.
+//   interleaved  tile n = rows [(blockIdx.x + n * gridDim.x) * BM, + BM): every CTA takes whole
+//                128-row tiles round-robin;
+//   contiguous   the CTA owns rows [row_begin, row_end), cut into full tiles followed by tail
+//                tiles of `tail_rows` rows (fetched through a second tensor map with that box
+//                height), so that all CTAs stream the same number of bytes although the tile
+//                count does not divide by the grid.  A tail tile still costs a full tile's MMAs
+//                (rows beyond it are stale shared memory whose results nobody reads).
+struct TileSched {
+  int row_begin, row_end, nfull, ntail, tail_rows, stride_rows;
+  __device__ __forceinline__ int count() const { return nfull + ntail; }
+  __device__ __forceinline__ bool is_tail(int n) const { return n >= nfull; }
+  __device__ __forceinline__ int row0(int n) const {
+    if (stride_rows) return row_begin + n * stride_rows;
+    return n < nfull ? row_begin + n * BM : row_begin + nfull * BM + (n - nfull) * tail_rows;
+  }
+  __device__ __forceinline__ int limit(int n) const {  // one past the last row of tile n that exists
+    const int r = row0(n) + (n < nfull ? BM : tail_rows);
+    return r < row_end ? r : row_end;
+  }
+};
+__device__ __forceinline__ TileSched sched_interleaved(int V) {
+  TileSched t;
+  const int ntiles = (V + BM - 1) / BM;
+  t.row_begin = (int)blockIdx.x * BM;
+  t.row_end = V;
+  t.nfull = (int)blockIdx.x < ntiles ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  t.ntail = 0;
+  t.tail_rows = 0;
+  t.stride_rows = (int)gridDim.x * BM;
+  return t;
+}
+// `per` rows per CTA (a multiple of 16); tail_rows = per % BM (0: the only partial tile is the one at V)
+__device__ __forceinline__ TileSched sched_contiguous(int V, int per) {
+  TileSched t;
+  const long long b = (long long)blockIdx.x * per;
+  t.row_begin = (int)(b < V ? b : V);
+  t.row_end = (int)(b + per < V ? b + per : V);
+  const int len = t.row_end - t.row_begin;
+  t.tail_rows = per % BM;
+  t.stride_rows = 0;
+  if (t.tail_rows) {
+    t.nfull = len / BM;
+    t.ntail = (len - t.nfull * BM + t.tail_rows - 1) / t.tail_rows;
+  } else {
+    t.nfull = (len + BM - 1) / BM;
+    t.ntail = 0;
+  }
+  return t;
+}
+
 __device__ __forceinline__ int ordered_key(float f) {  // order-preserving float -> signed int, NaN lowest
   if (f != f) return (int)0x80000000;
   int i = __float_as_int(f);
@@ -107,7 +163,8 @@ __device__ __forceinline__ float key_to_float(int k) {
 template <int EPI, int BN, int NI = 1>
 __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, int lane, uint32_t tmem_base,
                                               uint64_t* tfull, uint64_t* tempty, volatile int* abort_flag,
-                                              const RowMeta* meta, int* sstate, int ntiles) {
+                                              const RowMeta* meta, int* sstate, const TileSched& sched, Cand* qlists,
+                                              uint64_t* qlists_free) {
   constexpr bool INT8 = (EPI == 1);
   const int V = p.V, B = p.B;
     // ================================ epilogue =========================================
@@ -118,18 +175,28 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
     int* st_key = sstate + (size_t)(q * 3 + 1) * BN;   // best Gumbel score (ordered key)
     int* st_tok = sstate + (size_t)(q * 3 + 2) * BN;   // its local token id
     for (int b = lane; b < BN; b += 32) { st_max[b] = ordered_key(-INFINITY); st_key[b] = (int)0x80000000; st_tok[b] = 0x7fffffff; }
+    // decode-sized batches: the kListLen largest logits of every top-k column in this warp's rows
+    // (`qlists`: [4 warps][kTailMaxBatch][kListLen] entries of shared memory; when it is borrowed from a
+    // buffer the kernel's start-up still reads, `qlists_free` is the barrier that says it is done)
+    const bool use_lists = p.list_v != nullptr && qlists != nullptr;
+    Cand* ql = qlists + (size_t)q * kTailMaxBatch * kListLen;
+    if (use_lists) {
+      if (qlists_free) mbar_wait_warp(qlists_free, 0, abort_flag);
+      for (int i = lane; i < kTailMaxBatch * kListLen; i += 32) ql[i] = Cand{-INFINITY, 0x7fffffff};
+    }
     __syncwarp();
     float xs_w8a8 = 1.f;
     if constexpr (INT8) xs_w8a8 = *reinterpret_cast<const float*>(p.xscale);
     const int nchunk = (B + 15) / 16;
 
-    int tcount = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
+    const int mytiles = sched.count();
+    for (int tcount = 0; tcount < mytiles; ++tcount) {
       const int buf = (tcount % NI) * 2 + ((tcount / NI) & 1);
       const uint32_t tph = (uint32_t)((tcount / NI) >> 1) & 1u;
-      const int row = tile * BM + q * 32 + lane;
-      const bool rok = row < V;
-      const int rowc = rok ? row : V - 1;  // clamped: out-of-range lanes write nothing
+      const int tile_row0 = sched.row0(tcount), tile_lim = sched.limit(tcount);
+      const int row = tile_row0 + q * 32 + lane;
+      const bool rok = row < tile_lim;
+      const int rowc = rok ? row : tile_lim - 1;  // clamped: out-of-range lanes write nothing
       float rs = 1.f;
       if constexpr (EPI == 1) rs = reinterpret_cast<const float*>(p.wscale)[rowc];
       if constexpr (EPI == 0) rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[rowc]);
@@ -150,7 +217,7 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
         __half* cp = p.cand_logits + (long long)c0 * p.ld_cand + rowc;
         int mine_max = ordered_key(-INFINITY);
         tmem_ld_wait();
-        if (!p.bias && c0 + 16 <= B && (!p.do_sample || (candmask & 0xffffu) == 0xffffu)) {
+        if (!p.bias && !use_lists && c0 + 16 <= B && (!p.do_sample || (candmask & 0xffffu) == 0xffffu)) {
           // Fast path (all 16 columns exist and take the candidate path, or no sampling at all):
           // packed fp16 conversion, one store per column, and the 32-row maximum of every column
           // by a half2 butterfly over the warp instead of sixteen warp reductions.
@@ -226,8 +293,22 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
             if (lp && rok) lp[(long long)j * p.ld_logits] = h;
             if (candmask & (1u << j)) {
               if (rok) cp[(long long)j * p.ld_cand] = h;
-              const int mk = __reduce_max_sync(0xffffffffu, rok ? ordered_key(__half2float(h)) : ordered_key(-INFINITY));
-              if (lane == j) mine_max = mk;
+              if (use_lists) {
+                // lanes whose value beats the list's last entry hand it to lane 0, one after the other
+                const float l = __half2float(h);
+                Cand* e = ql + (c0 + j) * kListLen;
+                unsigned pass = __ballot_sync(0xffffffffu, rok && l > e[kListLen - 1].v);
+                while (pass) {
+                  const int src = __ffs(pass) - 1;
+                  pass &= pass - 1;
+                  const float v = __shfl_sync(0xffffffffu, l, src);
+                  if (lane == 0) list_insert(e, kListLen, v, tile_row0 + q * 32 + src);
+                  __syncwarp();
+                }
+              } else {
+                const int mk = __reduce_max_sync(0xffffffffu, rok ? ordered_key(__half2float(h)) : ordered_key(-INFINITY));
+                if (lane == j) mine_max = mk;
+              }
             } else if (livemask & (1u << j)) {
               const RowMeta m = meta[c0 + j];
               const float l = __half2float(h);
@@ -239,7 +320,7 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
               const int key = rok ? ordered_key(sc) : (int)0x80000000;
               const int mk = __reduce_max_sync(0xffffffffu, key);
               const unsigned eq = __ballot_sync(0xffffffffu, key == mk);
-              const int tok = tile * BM + q * 32 + (__ffs(eq) - 1);  // lowest row among equal scores
+              const int tok = tile_row0 + q * 32 + (__ffs(eq) - 1);  // lowest row among equal scores
               if (lane == j && (mk > st_key[c0 + j] || (mk == st_key[c0 + j] && tok < st_tok[c0 + j]))) {
                 st_key[c0 + j] = mk;
                 st_tok[c0 + j] = tok;
@@ -258,10 +339,16 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
       const int slice = blockIdx.x * 4 + q;
       for (int b = lane; b < B; b += 32) {
         const long long o = (long long)b * p.nslices + slice;
-        p.slice_max[o] = key_to_float(st_max[b]);
+        p.slice_max[o] = use_lists ? ql[b * kListLen].v : key_to_float(st_max[b]);
         p.part_score[o] = st_key[b] == (int)0x80000000 ? -INFINITY : key_to_float(st_key[b]);
         p.part_token[o] = st_tok[b];
       }
+      if (use_lists)
+        for (int i = lane; i < B * kListLen; i += 32) {
+          const int b = i / kListLen, pos = i % kListLen;
+          p.list_v[((long long)b * kListLen + pos) * p.nslices + slice] = ql[i].v;
+          if (pos < kListM) p.list_t[((long long)b * kListM + pos) * p.nslices + slice] = ql[i].t;
+        }
     }
 }
 

@@ -30,6 +30,32 @@ int require_sm100();    // VQK_OK or VQK_ERR_ARCH
 
 constexpr int GROUP = 32;  // MX block size (reference: _kernels.py:488,646)
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// The lm_head kernels follow the activation quantizer on the stream.  Launched as its
+// programmatic dependents they start while it still runs (barrier set-up, TMEM allocation, the
+// first weight loads need nothing from it) and wait right before they first touch its output;
+// the quantizer lets them go at its own start.  Both instructions are no-ops in a kernel that was
+// launched the plain way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool pdl_enabled();  // VQK_PDL=0 switches it off (A/B runs)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- numeric helpers ------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);

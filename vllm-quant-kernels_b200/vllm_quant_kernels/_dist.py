@@ -22,7 +22,7 @@ import numpy as np
 import torch
 
 from . import _ffi
-from ._lmhead import LMHeadShard, SamplingArgs, finalize_records
+from ._lmhead import LMHeadShard, SamplingArgs, finalize_records, sample_logits
 
 ROW_ALIGN = 16  # shard boundaries fall on the kernels' 16-row tiles
 
@@ -125,6 +125,11 @@ class VqkPeer:
                     torch.cuda.current_stream(rec.device).cuda_stream))
         return tokens, scores
 
+    def set_wait_limit(self, polls: int) -> None:
+        """Bound of every wait for a peer's words, in polls (the default is about a second).  A
+        wait that runs out gives the row token -1 and raises `vqk_device_error`."""
+        _ffi.check(_ffi.lib().vqk_peer_set_wait_limit(self._h, int(polls)))
+
     def close(self):
         if self._h:
             _ffi.lib().vqk_peer_destroy(self._h)
@@ -164,14 +169,69 @@ class VocabShardedLMHead:
         return SamplingArgs(sp.temperature, sp.seeds, sp.top_k, sp.top_p, sp.topk_threshold,
                             vocab_offset=self.vocab_start, vocab_total=self.vocab_total)
 
-    def step(self, hidden_states: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None):
-        """(tokens int64 [B], scores fp32 [B]), identical on every rank."""
+    def step(self, hidden_states: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None,
+             unresolved: str = "leave"):
+        """(tokens int64 [B], scores fp32 [B]), identical on every rank.
+
+        The one-exchange merge decides a row from the ranks' 1 KiB records.  A row whose record
+        cannot hold what the merge needs - top-p without top-k (vLLM also marks a disabled top-k
+        as k = vocab size), or more than 126 top-k survivors on one shard - comes back as token
+        -1.  `unresolved` says what to do about it:
+          "leave"  return the -1 (no host synchronisation: safe inside a CUDA-graph capture);
+          "raise"  synchronise, raise RuntimeError if any row is -1;
+          "rerun"  synchronise, and resolve the -1 rows exactly: their fp16 shard logits are
+                   all-gathered (torch.distributed, 0.5 MB per row at 248320 columns) and the
+                   single-shard sampler runs on the full rows; every rank gets the same tokens.
+        """
+        if unresolved not in ("leave", "raise", "rerun"):
+            raise ValueError("unresolved must be 'leave', 'raise' or 'rerun'")
         lsp = self.local_args(sp)
-        rec = self.shard.shard_records(hidden_states, lsp, bias)
         if self.peer is not None:
-            return self.peer.exchange_finalize(rec, lsp)
-        gathered = exchange_records(rec, self.group, self.comm)
-        return finalize_records(gathered, lsp)
+            tokens, scores = self.shard.step_sharded(hidden_states, lsp, self.peer._h, bias)
+        else:
+            rec = self.shard.shard_records(hidden_states, lsp, bias)
+            gathered = exchange_records(rec, self.group, self.comm)
+            tokens, scores = finalize_records(gathered, lsp)
+        if unresolved == "leave":
+            return tokens, scores
+        missing = torch.nonzero(tokens < 0).flatten()      # host synchronisation
+        if missing.numel() == 0:
+            return tokens, scores
+        if unresolved == "raise":
+            raise RuntimeError(f"rows {missing.tolist()} cannot be merged from the shard records "
+                               "(top-p without top-k, or more than 126 top-k survivors on a shard)")
+        t2, s2 = self.resolve_rows(hidden_states, sp, missing, bias)
+        tokens = tokens.clone()
+        scores = scores.clone()
+        tokens[missing] = t2
+        scores[missing] = s2
+        return tokens, scores
+
+    def resolve_rows(self, hidden_states: torch.Tensor, sp: SamplingArgs, rows: torch.Tensor,
+                     bias: Optional[torch.Tensor] = None):
+        """Exact sampling of the given batch rows from the FULL logits rows: every rank computes its
+        fp16 logits slice of those rows, the slices are all-gathered (torch.distributed on
+        `self.group`), and the single-shard sampler runs on the concatenation.  All ranks must
+        call it with the same rows."""
+        import torch.distributed as dist
+        x = hidden_states.reshape(-1, self.shard.H)[rows]
+        local = self.shard.logits(x, bias)                                   # [n, V_local]
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        per = shard_bounds(self.vocab_total, world, 0)[1]
+        padded = torch.full((local.shape[0], per), float("-inf"), dtype=local.dtype, device=local.device)
+        padded[:, :local.shape[1]] = local
+        if world > 1:
+            parts = torch.empty((world,) + tuple(padded.shape), dtype=padded.dtype, device=padded.device)
+            dist.all_gather_into_tensor(parts, padded, group=self.group)
+        else:
+            parts = padded.unsqueeze(0)
+        full = parts.permute(1, 0, 2).reshape(local.shape[0], world * per)[:, :self.vocab_total].contiguous()
+
+        def pick(t):
+            return None if t is None else t[rows].contiguous()
+        rsp = SamplingArgs(pick(sp.temperature), pick(sp.seeds), pick(sp.top_k), pick(sp.top_p),
+                           pick(sp.topk_threshold), 0, self.vocab_total)
+        return sample_logits(full, rsp)
 
 
 # ---- record layout helpers (host side; used by tools and tests) -----------------------

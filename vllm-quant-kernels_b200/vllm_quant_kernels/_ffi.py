@@ -25,12 +25,15 @@ STATIC_MAX_VOCAB = 262144
 
 # every symbol include/vqk.h declares
 SYMBOLS = (
-    "vqk_version", "vqk_strerror", "vqk_last_cuda_error", "vqk_device_error", "vqk_quantize_weight", "vqk_quantize_act",
+    "vqk_version", "vqk_strerror", "vqk_last_cuda_error", "vqk_device_error", "vqk_device_error_clear",
+    "vqk_quantize_weight", "vqk_quantize_act",
     "vqk_lm_head_create", "vqk_lm_head_destroy", "vqk_lm_head_workspace_bytes", "vqk_lm_head_forward",
-    "vqk_lm_head_set_kernel_events",
+    "vqk_lm_head_set_kernel_events", "vqk_lm_head_set_debug_times",
     "vqk_sample_workspace_bytes", "vqk_sample", "vqk_sample_static", "vqk_sample_finalize", "vqk_topk_threshold",
     "vqk_comm_unique_id", "vqk_comm_create", "vqk_comm_allgather", "vqk_comm_destroy",
-    "vqk_peer_create", "vqk_peer_connect", "vqk_peer_exchange_finalize", "vqk_peer_destroy",
+    "vqk_peer_create", "vqk_peer_connect", "vqk_peer_connect_pointers", "vqk_peer_local_buffer",
+    "vqk_peer_set_wait_limit", "vqk_lm_head_step_sharded_workspace_bytes", "vqk_lm_head_step_sharded",
+    "vqk_peer_exchange_finalize", "vqk_peer_destroy",
 )
 
 
@@ -75,6 +78,7 @@ def lib() -> ctypes.CDLL:
         c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, POINTER(SampleParams),
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     L.vqk_lm_head_set_kernel_events.argtypes = [c_void_p, c_void_p, c_void_p]
+    L.vqk_lm_head_set_debug_times.argtypes = [c_void_p, c_void_p]
     L.vqk_sample_workspace_bytes.restype = c_int64
     L.vqk_sample_workspace_bytes.argtypes = [c_int64, c_int64]
     L.vqk_sample.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int64, POINTER(SampleParams), c_void_p, c_void_p,
@@ -92,6 +96,16 @@ def lib() -> ctypes.CDLL:
     L.vqk_peer_exchange_finalize.argtypes = [c_void_p, c_void_p, c_int64, POINTER(SampleParams), c_void_p, c_void_p,
                                              c_void_p]
     L.vqk_peer_destroy.argtypes = [c_void_p]
+    L.vqk_device_error_clear.restype = c_int
+    L.vqk_peer_connect_pointers.argtypes = [c_void_p, POINTER(c_void_p)]
+    L.vqk_peer_local_buffer.restype = c_void_p
+    L.vqk_peer_local_buffer.argtypes = [c_void_p]
+    L.vqk_peer_set_wait_limit.argtypes = [c_void_p, c_int64]
+    L.vqk_lm_head_step_sharded_workspace_bytes.restype = c_int64
+    L.vqk_lm_head_step_sharded_workspace_bytes.argtypes = [c_void_p, c_int64]
+    L.vqk_lm_head_step_sharded.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, POINTER(SampleParams), c_void_p, c_void_p,
+        c_void_p, c_int64, c_void_p]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if fn.restype is c_int and name not in ("vqk_version", "vqk_last_cuda_error", "vqk_device_error"):

@@ -267,6 +267,36 @@ class LMHeadShard:
             self._forward(x2, bias, out, sp, tokens, scores, None)
         return (tokens, scores, out) if return_logits else (tokens, scores)
 
+    def step_sharded(self, x: torch.Tensor, sp: SamplingArgs, peer_handle, bias: Optional[torch.Tensor] = None):
+        """This rank's part of a vocab-sharded step in ONE library call: lm_head shard, local
+        sampling stage, record exchange over peer memory and merge (`vqk_lm_head_step_sharded`).
+        `sp` carries this rank's vocab_offset and the global vocab_total; `peer_handle` is a
+        connected vqk_peer.  Returns the merged (tokens, scores), identical on every rank."""
+        x2 = self._x2d(x)
+        B = x2.shape[0]
+        tokens = torch.empty(B, dtype=torch.int64, device=self.device)
+        scores = torch.empty(B, dtype=torch.float32, device=self.device)
+        if bias is not None:
+            bias = bias.to(torch.float16).contiguous()
+        if not B:
+            return tokens, scores
+        L = _ffi.lib()
+        key = ("sharded", B)
+        n = self._ws_bytes.get(key)
+        if n is None:
+            with torch.cuda.device(self.device):
+                n = int(L.vqk_lm_head_step_sharded_workspace_bytes(self._h, B))
+            if n < 0:
+                _ffi.check(n)
+            self._ws_bytes[key] = n
+        ws = self._wsp.get(self.device, n)
+        spc = sp.to_c(B, self.V)
+        with torch.cuda.device(self.device):
+            _ffi.check(L.vqk_lm_head_step_sharded(self._h, peer_handle, x2.data_ptr(), _DT[x2.dtype], B, x2.stride(0),
+                                                  _ptr(bias), ctypes.byref(spc), tokens.data_ptr(), scores.data_ptr(),
+                                                  ws.data_ptr(), n, _stream(x2)))
+        return tokens, scores
+
     def shard_records(self, x: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """lm_head + local sampling stage of a vocab-sharded step: uint8 [B, 1024]
         exchange records to be all-gathered and passed to `finalize_records`."""
