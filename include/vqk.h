@@ -160,6 +160,14 @@ int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, int64_t B, i
                         const vqk_sample_params* sp, int64_t* tokens, float* scores, void* records,
                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The post-ops vLLM's LogitsProcessor.forward applies to the logits after the matmul and the bias
+ * (vllm/model_executor/layers/logits_processor.py:66-72; the reference left them to upstream, i.e.
+ * to extra passes over [B, V]): soft_cap > 0 -> tanh(logits / soft_cap) * soft_cap, then
+ * logits *= scale.  Set on the handle, applied in the epilogue of every following
+ * vqk_lm_head_forward with upstream's fp16 roundings (each of its tensor ops rounds to fp16), so
+ * both the logits written and the tokens sampled see them.  (0, 1) switches them off. */
+int vqk_lm_head_set_post_ops(vqk_lm_head* h, float soft_cap, float scale);
+
 /* Measurement aid (no counterpart in the reference): when both are non-NULL cudaEvent_t
  * handles, every following vqk_lm_head_forward on `h` records `start` right before and
  * `stop` right after its weight-streaming kernel launch(es) on the call's stream, so a

@@ -206,3 +206,49 @@ def test_topk_threshold_wrapper_matches_torch_topk():
     for i, ki in enumerate(k.tolist()):
         want = logits[i].topk(ki).values[-1].item() if 0 < ki < V else -np.inf
         assert thr[i].item() == want
+
+
+@pytest.mark.gpu
+def test_try_fused_step_equals_the_two_hooks(monkeypatch):
+    """`try_fused_step` (lm_head + sampler in one pass) against what the two plugin hooks give on
+    the same inputs: `_quantized_forward` -> fp32 cast -> the CUDA sampler, same seeds."""
+    from types import SimpleNamespace
+    from tests.util import make_act, make_weight
+    from vllm_quant_kernels import _lmhead as LH
+    from vllm_quant_kernels._quant import QuantizedLogitsProcessor
+    from vllm_quant_kernels._sampler import try_fused_step
+
+    class FakeWeight:
+        def __init__(self, t):
+            self.data, self.dtype, self.shape, self.device = t, t.dtype, t.shape, t.device
+    V, H, B = 100_016, 256, 6
+    w = make_weight(V, H, seed=71) * 8.0
+    x = make_act(B, H, seed=72)
+    for e in ("VLLM_USE_W8A8_LMHEAD", "VLLM_USE_FP8_LMHEAD", "VLLM_USE_MXFP8_LMHEAD", "VLLM_USE_MXFP4_LMHEAD"):
+        monkeypatch.delenv(e, raising=False)
+    lm = SimpleNamespace(weight=FakeWeight(w))
+    proc = QuantizedLogitsProcessor.__new__(QuantizedLogitsProcessor)
+    proc.soft_cap, proc.scale, proc.logits_as_input, proc.org_vocab_size = 25.0, 1.0, False, V - 16
+    seeds = torch.arange(B, dtype=torch.int32, device="cuda") + 100
+    T = torch.tensor([0.0, 0.7, 0.9, 1.0, 1.2, 1.4])
+    top_k = torch.tensor([50, 50, 10, V, 5, 50], dtype=torch.int32, device="cuda")
+    top_p = torch.tensor([0.9, 0.9, 1.0, 0.8, 0.95, 0.5], dtype=torch.float32, device="cuda")
+    sm = _make_sampling_metadata(B, V, temperature=T, top_k=top_k, top_p=top_p)
+    sm.all_random = False
+    tok = try_fused_step(proc, lm, x, sm, seeds=seeds)
+    assert tok is not None and tok.dtype == torch.int64 and tok.shape == (B,)
+    logits = proc.forward(lm, x).to(torch.float32)                    # soft-capped, padding trimmed
+    assert logits.shape == (B, V - 16)
+    want, _ = LH.sample_logits(logits, LH.SamplingArgs(T.cuda(), seeds, top_k, top_p))
+    assert torch.equal(tok, want)
+    assert tok[0] == logits[0].argmax()
+    # off the fused path: logprobs wanted, penalties, a generator -> None (the runner falls back)
+    assert try_fused_step(proc, lm, x, _make_sampling_metadata(B, V, temperature=T, max_num_logprobs=3)) is None
+    sm2 = _make_sampling_metadata(B, V, temperature=T)
+    sm2.no_penalties = False
+    assert try_fused_step(proc, lm, x, sm2) is None
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    assert try_fused_step(proc, lm, x, _make_sampling_metadata(B, V, temperature=T, generators={0: gen})) is None
+    # all greedy
+    tok = try_fused_step(proc, lm, x, _make_sampling_metadata(B, V, all_greedy=True))
+    assert torch.equal(tok, logits.argmax(-1))

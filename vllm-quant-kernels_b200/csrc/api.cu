@@ -74,8 +74,7 @@ struct LmHeadWs {
   float* slice_max;
   float* part_score;
   int* part_token;
-  float* list_v;  // decode-sized batches only
-  int* list_t;
+  SliceList* lists;  // decode-sized batches only
   int* row_flag;
   __half* cand;
   long long ld_cand;
@@ -132,10 +131,7 @@ static LmHeadWs carve_lm_head(void* base, int mode, long long V, long long K, lo
     w.slice_max = c.take<float>((size_t)B * nslices);
     w.part_score = c.take<float>((size_t)B * nslices);
     w.part_token = c.take<int>((size_t)B * nslices);
-    if (B <= kTailMaxBatch) {
-      w.list_v = c.take<float>((size_t)B * nslices * kListLen);
-      w.list_t = c.take<int>((size_t)B * nslices * kListM);
-    }
+    if (B <= kTailMaxBatch) w.lists = c.take<SliceList>((size_t)B * nslices);
     w.row_flag = c.take<int>((size_t)B);
     w.ld_cand = (V + 7) & ~7LL;
     w.cand = c.take<__half>((size_t)B * w.ld_cand);
@@ -159,6 +155,7 @@ struct vqk_lm_head {
   cudaEvent_t ev_start, ev_stop;
   int ticket_slot;
   unsigned long long* dbg;
+  float soft_cap, out_scale;
 };
 
 extern "C" int vqk_version(void) { return VQK_VERSION; }
@@ -207,6 +204,7 @@ extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, i
   if (!h) return VQK_ERR_INVALID;
   h->mode = mode; h->q = (const uint8_t*)q; h->scales = scales; h->V = V; h->H = H;
   h->ev_start = nullptr; h->ev_stop = nullptr; h->dbg = nullptr;
+  h->soft_cap = 0.f; h->out_scale = 1.f;
   static unsigned int next_slot = 0;
   h->ticket_slot = (int)(__atomic_fetch_add(&next_slot, 1u, __ATOMIC_RELAXED) % kTicketSlots);
   *out = h;
@@ -222,6 +220,13 @@ extern "C" int vqk_lm_head_set_kernel_events(vqk_lm_head* h, void* start_event, 
   if (!h || (!start_event != !stop_event)) return VQK_ERR_INVALID;
   h->ev_start = (cudaEvent_t)start_event;
   h->ev_stop = (cudaEvent_t)stop_event;
+  return VQK_OK;
+}
+
+extern "C" int vqk_lm_head_set_post_ops(vqk_lm_head* h, float soft_cap, float scale) {
+  if (!h || soft_cap != soft_cap || scale != scale) return VQK_ERR_INVALID;
+  h->soft_cap = soft_cap > 0.f ? soft_cap : 0.f;
+  h->out_scale = scale;
   return VQK_OK;
 }
 
@@ -308,8 +313,11 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   }();
   const bool fuse_tail = tail_mode && sp && B <= kTailMaxBatch && B <= maxcols && nslices <= 1024;
   unsigned int* tickets = nullptr;
+  int* error_word = nullptr;
   if (fuse_tail) {
     rc = ticket_base(&tickets);
+    if (rc) return rc;
+    rc = peer_error_word(&error_word);
     if (rc) return rc;
   }
 
@@ -333,6 +341,8 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
     p.dbg = h->dbg;
     p.pdl = (mode != VQK_MODE_W8A16 && b0 == 0 && pdl_enabled()) ? 1 : 0;
     p.bias = (const __half*)bias;
+    p.soft_cap = h->soft_cap;
+    p.out_scale = h->out_scale;
     p.logits = logits ? (__half*)logits + (size_t)b0 * ld_logits : nullptr;
     p.ld_logits = ld_logits;
     p.do_sample = sp ? 1 : 0;
@@ -353,9 +363,9 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
       }
       if (fuse_tail) {
         p.fuse_tail = tail_mode;
-        p.list_v = ws.list_v;
-        p.list_t = ws.list_t;
+        p.lists = ws.lists;
         p.ticket = tickets + h->ticket_slot;
+        p.error = error_word;
         p.row_flag = ws.row_flag;
         p.tokens = (long long*)tokens; p.scores = scores; p.records = (uint8_t*)records;
         p.single_shard = (tokens && !peer) ? 1 : 0;

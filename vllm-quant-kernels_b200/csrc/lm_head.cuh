@@ -5,6 +5,16 @@
 
 namespace vqk {
 
+constexpr int kListM = 4;            // entries of a slice list that can be used ...
+constexpr int kListLen = kListM + 1;  // ... plus the witness: every logit of the slice outside the list is <= it
+// what an epilogue leaves per (row, slice) for the tail: two 16-byte words
+struct __align__(16) SliceList {
+  int t[kListM];       // local token ids of the kListM largest logits
+  __half v[kListLen];  // their values, descending, then the witness
+  __half pad[3];
+};
+static_assert(sizeof(SliceList) == 32, "two 16-byte loads per slice");
+
 // Record exchange over peer memory (peer_exchange.cuh).  G == 0: no exchange.
 struct PeerTable {
   unsigned long long* land[8];  // every rank's landing buffer [2][G][max_rows][kWireWords] words (own one included)
@@ -23,6 +33,8 @@ struct LmHeadParams {
   int V, K, B;
   long long ldx;
   const __half* bias;  // [V] or null
+  float soft_cap;      // > 0: logits = tanh(logits / soft_cap) * soft_cap after the bias (0: off)
+  float out_scale;     // logits *= out_scale after that (1: off)
   __half* logits;      // [B, ld_logits] or null
   long long ld_logits;
   int do_sample;
@@ -37,9 +49,9 @@ struct LmHeadParams {
   unsigned long long* dbg;  // null, or [gridDim.x][16] time stamps (vqk_lm_head_set_debug_times)
   // decode-sized batches: the last CTA to finish resolves the rows (tail.cuh)
   int fuse_tail;
-  float* list_v;         // [B][kListLen][nslices] largest logits per slice, descending; position kListM is the witness
-  int* list_t;           // [B][kListM][nslices] their LOCAL token ids (null together with list_v: no lists)
+  SliceList* lists;      // [B][nslices] largest logits per slice with LOCAL token ids (top-k rows); null: no lists
   unsigned int* ticket;  // device counter, zero between launches
+  int* error;            // device error word, set when the tail's bounded wait for the grid runs out
   int* row_flag;         // [B] written by the tail: 1 = the row still needs the full-row kernel
   long long* tokens;     // outputs of the tail (as SelectParams)
   float* scores;
@@ -47,6 +59,20 @@ struct LmHeadParams {
   int single_shard;
   PeerTable peer;        // sharded step: the tail also exchanges the row's record and merges (G > 0)
 };
+
+// vLLM's LogitsProcessor.forward post-ops (vllm/model_executor/layers/logits_processor.py:66-72) on an
+// fp16 logit, with upstream's roundings: it runs them as separate fp16 tensor ops (divide, tanh,
+// multiply, multiply), each computed in fp32 and rounded to fp16; torch turns the division of a
+// tensor by a host scalar into a multiplication by the scalar's fp32 reciprocal.
+__device__ __forceinline__ __half logit_post_ops(__half h, float soft_cap, float out_scale) {
+  if (soft_cap > 0.f) {
+    h = __float2half_rn(__half2float(h) * __fdiv_rn(1.0f, soft_cap));
+    h = __float2half_rn(tanhf(__half2float(h)));
+    h = __float2half_rn(__half2float(h) * soft_cap);
+  }
+  if (out_scale != 1.f) h = __float2half_rn(__half2float(h) * out_scale);
+  return h;
+}
 
 // time stamp i of this CTA (measurement aid; %globaltimer, nanoseconds)
 __device__ __forceinline__ void dbg_stamp(const LmHeadParams& p, int i) {
@@ -57,8 +83,7 @@ __device__ __forceinline__ void dbg_stamp(const LmHeadParams& p, int i) {
   }
 }
 
-constexpr int kListM = 4;            // entries of a slice list that can be used ...
-constexpr int kListLen = kListM + 1;  // ... plus the witness: every logit of the slice outside the list is <= it
+
 constexpr int kTailMaxBatch = 16;    // largest batch whose rows the lm_head kernel resolves itself
 
 // lm_head_stream.cu

@@ -385,6 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
         else v = s * rs;
         __half h = __float2half_rn(v);
         if (p.bias) h = __float2half_rn(__half2float(h) + bias);
+        h = logit_post_ops(h, p.soft_cap, p.out_scale);
         if (p.logits) p.logits[(long long)b * p.ld_logits + row] = h;
         if (p.do_sample) {
           const RowMeta m = meta[b];
@@ -437,12 +438,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
       const int b = nt * 8 + ec;
       if (b < B) {
         const long long o = (long long)b * p.nslices + slice;
-        if (p.list_v && er < kListLen) {  // row-thread i of the column writes list entry i
-          const Cand mine = slist[b * kListLen + er];
-          p.list_v[((long long)b * kListLen + er) * p.nslices + slice] = mine.v;
-          if (er < kListM) p.list_t[((long long)b * kListM + er) * p.nslices + slice] = mine.t;
-        }
         if (er == 0) {
+          if (p.lists) {
+            SliceList rec;
+#pragma unroll
+            for (int i = 0; i < kListLen; ++i) {
+              const Cand c = slist[b * kListLen + i];
+              rec.v[i] = __float2half_rn(c.v);
+              if (i < kListM) rec.t[i] = c.t;
+            }
+            rec.pad[0] = rec.pad[1] = rec.pad[2] = __float2half_rn(0.f);
+            p.lists[o] = rec;
+          }
           p.slice_max[o] = slist[b * kListLen].v;
           p.part_score[o] = s;
           p.part_token[o] = tk;

@@ -1,6 +1,6 @@
-// Sampler tail of the decode-sized lm_head kernels: the LAST CTA of the grid to finish (an atomic
-// ticket; nobody waits for anybody) turns the per-slice results every CTA left in memory into
-// the step's tokens, one warp per batch row, while those results are still in L2.
+// Sampler tail of the decode-sized lm_head kernels: one CTA of the grid turns the per-slice results
+// every CTA left in memory into the step's tokens, one warp per batch row, while those results are
+// still in L2.
 //
 // Per (row, slice) the epilogues leave
 //   * part_score / part_token   Gumbel (or greedy) winner of the slice, for rows without top-k / top-p;
@@ -17,10 +17,18 @@
 // row by the full-row kernel (k_select), which is launched behind every step and returns at once
 // for rows whose flag is 0.
 //
-// The warp keeps its working sets in registers (a row's slice heads, the staged list entries, the
-// union of the shards' candidates) and fetches them with unrolled batches of independent loads:
-// the tail is a chain of L2 latencies, not of instructions.  All logits on this path are fp16
-// values, so their order is the order of 16-bit keys.
+// WHO runs it: the LAST CTA of the grid to finish (an atomic ticket; nobody waits for anybody).
+// HOW it is written: a single warp runs at the speed of its dependent latencies, not of its
+// instruction count - an L2 round trip costs it more than a microsecond, a shared-memory bisection
+// round some three hundred cycles.  (Measured on B200 with %globaltimer stamps: a version that
+// walked the data in small loops took 16 us per row, one with everything unrolled 21 us; running
+// either twice on the same SM did not make the second run faster, so it is not instruction fetch.)
+// So a row costs TWO dependent L2 trips - the slice maxima, four to a 16-byte load, then the
+// 32-byte list records of the few CTAs whose maximum can matter - and the selections run on
+// registers: the k-th largest of the 148 per-CTA maxima bounds the k-th largest logit from below
+// as the k-th largest slice maximum does, with a quarter of the keys.
+//
+// All logits on this path are fp16 values, so their order is the order of 16-bit keys.
 #pragma once
 
 #include "lm_head.cuh"
@@ -28,33 +36,35 @@
 
 namespace vqk {
 
-constexpr int kTailMaxSlices = 1024;  // slices per row the tail can take (148 SMs x 4 = 592)
-constexpr int kTailHeadRegs = kTailMaxSlices / 32;
+constexpr int kTailMaxSlices = 1024;  // slices per row the tail can take (148 SMs x 4 = 592); a multiple of 4
+constexpr int kTailQuadRegs = kTailMaxSlices / 4 / 32;  // 16-byte loads of slice maxima per lane
 constexpr int kTailMaxK = 126;        // largest top-k resolved from the lists (a shard record holds as many)
-constexpr int kTailSliceCap = 160;    // slices whose head can reach the k-th largest (k + ties)
-constexpr int kTailStageCap = kTailSliceCap * kListM;
-constexpr int kTailStageRegs = kTailStageCap / 32;
+constexpr int kTailQuadCap = 128;     // CTAs (quads of slices) whose maximum can reach the k-th largest (k + ties)
+constexpr int kTailRecRegs = 8;       // list records per lane and round: 64 CTAs' worth
+constexpr int kTailStageCap = 1024;   // listed values >= tau0 a row may stage
 constexpr int kTailSurvCap = 192;     // survivors of top-k (k + ties) resolved per row
-constexpr int kTailSurvRegs = kTailSurvCap / 32;
 constexpr int kTailMaxWarps = 16;
-constexpr int kMergeRegs = (kMergeCap + 31) / 32;
 
-// Per-warp scratch (bytes).  Region A holds the slice ids and staged list entries while a row is
-// resolved from the lists, and afterwards the union of the shards' candidates (mv, mt); the
-// survivors (cv, ct) follow it.
-constexpr int kTailOffSlices = 0;                                   // uint16 [kTailSliceCap]
-constexpr int kTailOffStage = kTailOffSlices + kTailSliceCap * 2;    // uint32 [kTailStageCap]: key << 16 | entry index
+// Per-warp scratch (bytes).  Region A holds the head keys, slice ids and staged list entries while
+// a row is resolved from the lists, and afterwards the union of the shards' candidates (mv, mt);
+// region B holds the survivors and the top-p work arrays.
+constexpr int kTailOffQuads = 0;                                    // uint16 [kTailQuadCap]
+constexpr int kTailOffStage = kTailOffQuads + kTailQuadCap * 2;      // uint2  [kTailStageCap]: key, local token
 constexpr int kTailOffMv = 0;                                       // float  [kMergeCap]
 constexpr int kTailOffMt = kTailOffMv + kMergeCap * 4;              // int    [kMergeCap]
-constexpr int kTailRegionA = kTailOffMt + kMergeCap * 4;
-static_assert(kTailOffStage + kTailStageCap * 4 <= kTailRegionA, "list staging fits region A");
+constexpr int kTailRegionA = ((kTailOffMt + kMergeCap * 4 > kTailOffStage + kTailStageCap * 8 ? kTailOffMt + kMergeCap * 4
+                                                                                              : kTailOffStage + kTailStageCap * 8) + 15) & ~15;
 constexpr int kTailOffCv = kTailRegionA;                            // float  [kTailSurvCap]
 constexpr int kTailOffCt = kTailOffCv + kTailSurvCap * 4;           // int    [kTailSurvCap]
-constexpr int kTailWarpBytes = (kTailOffCt + kTailSurvCap * 4 + 15) & ~15;
+constexpr int kTailOffY = kTailOffCt + kTailSurvCap * 4;            // float  [kTailSurvCap]
+constexpr int kTailOffW = kTailOffY + kTailSurvCap * 4;             // uint64 [kTailSurvCap]
+constexpr int kTailOffAlive = kTailOffW + kTailSurvCap * 8;         // uint8  [kTailSurvCap]
+constexpr int kTailWarpBytes = (kTailOffAlive + kTailSurvCap + 15) & ~15;
+static_assert(kTailOffW % 8 == 0, "mass array alignment");
 
-// shared memory the tail wants from a CTA of `warps` warps (it makes do with less: fewer rows at a time)
-__host__ __device__ inline size_t tail_smem_bytes(int warps) {
-  return (size_t)(warps < kTailMaxWarps ? warps : kTailMaxWarps) * kTailWarpBytes;
+// shared memory the tail wants from a CTA for `rows` batch rows (it makes do with less: fewer rows at a time)
+__host__ __device__ inline size_t tail_smem_bytes(int rows) {
+  return (size_t)(rows < kTailMaxWarps ? rows : kTailMaxWarps) * kTailWarpBytes;
 }
 
 // order-preserving 16-bit key of an fp16-representable float; -0 sorts with +0
@@ -69,19 +79,17 @@ __device__ __forceinline__ float h16_key_to_float(uint32_t k) {
 }
 constexpr uint32_t kKeyLowestFinite = 0x0400u;  // key(-65504); key(-inf) = 0x03ff sorts below
 
-// k-th largest of the keys a warp holds in registers, key[j] of lane l being element j * 32 + l
-// (unused slots hold a key below every candidate), by bisection on the key bits `hi` down to
-// `lo`: the largest x with count(key >= x) >= k.  Result in every lane.
-template <int R>
-__device__ __forceinline__ uint32_t warp_kth_largest_reg(const uint32_t (&key)[R], int used, int k, int hi, int lo) {
+// k-th largest of n keys in shared memory (n >= k >= 1) by bisection on the key bits `hi` down to
+// `lo`: the largest x with count(key >= x) >= k.  Whole warp; result in every lane.
+template <typename LoadKey>
+__device__ __forceinline__ uint32_t warp_kth_largest_key(LoadKey key_at, int n, int k, int hi, int lo, int lane) {
   uint32_t prefix = 0;
 #pragma unroll 1
   for (int bit = hi; bit >= lo; --bit) {
     const uint32_t cand = prefix | (1u << bit);
     int c = 0;
-#pragma unroll
-    for (int j = 0; j < R; ++j)
-      if (j < used) c += (key[j] >= cand);
+#pragma unroll 4
+    for (int i = lane; i < n; i += 32) c += (key_at(i) >= cand);
     c = __reduce_add_sync(0xffffffffu, c);
     if (c >= k) prefix = cand;
   }
@@ -105,28 +113,18 @@ __device__ __forceinline__ void tail_write_header(uint8_t* records, int b, float
 
 // Top-k over n <= kMergeCap candidates (raw logit, token) in shared memory, in place: those >= the
 // K-th largest (ties kept; all of them when n <= K or K <= 0) move to the front.  Returns how many.
-__device__ inline int warp_topk_inplace(float* v, int* t, int n, int K, int lane) {
+static __device__ __noinline__ int warp_topk_inplace(float* v, int* t, int n, int K, int lane) {
   if (K <= 0 || n <= K) return n;
-  uint32_t key[kMergeRegs];
-  const int used = (n + 31) >> 5;
-  int low = 1;
-#pragma unroll
-  for (int j = 0; j < kMergeRegs; ++j) {
-    key[j] = 0;
-    if (j < used && j * 32 + lane < n) {
-      const float x = v[j * 32 + lane];
-      key[j] = f32_key(x);
-      low &= ((__float_as_uint(x) & 0x1fffu) == 0);
-    }
-  }
   // fp16-representable values (every logit of the lm_head path) differ in the upper 19 key bits only
+  int low = 1;
+  for (int i = lane; i < n; i += 32) low &= ((__float_as_uint(v[i]) & 0x1fffu) == 0);
   low = __all_sync(0xffffffffu, low);
-  const uint32_t tk = warp_kth_largest_reg(key, used, K, 31, low ? 13 : 0);
+  const uint32_t tk = warp_kth_largest_key([&](int i) { return f32_key(v[i]); }, n, K, 31, low ? 13 : 0, lane);
   const unsigned lt = (1u << lane) - 1u;
   int kept = 0;
 #pragma unroll 1
-  for (int j = 0; j < used; ++j) {
-    const int i = j * 32 + lane;
+  for (int i0 = 0; i0 < n; i0 += 32) {
+    const int i = i0 + lane;
     float vi = 0.f;
     int ti = 0;
     bool keep = false;
@@ -139,66 +137,53 @@ __device__ inline int warp_topk_inplace(float* v, int* t, int n, int K, int lane
   return kept;
 }
 
-// Top-p over the n <= kTailSurvCap top-k survivors (shared memory), then the Gumbel argmax: the
-// arithmetic of resolve_candidates (sampler.cu), so both paths pick the same token with the same
-// score.  The survivors sit in registers; the mass above each one is summed over shuffles.
-__device__ inline void warp_topp_gumbel(const float* cv, const int* ct, int n, const RowMeta& m, int lane, float& s,
-                                        int& t) {
-  float y[kTailSurvRegs];
-  int tok[kTailSurvRegs];
-  bool alive[kTailSurvRegs];
-  const int used = (n + 31) >> 5;
-#pragma unroll
-  for (int j = 0; j < kTailSurvRegs; ++j) {
-    const int i = j * 32 + lane;
-    alive[j] = j < used && i < n;
-    y[j] = alive[j] ? cv[i] / m.T : -INFINITY;
-    tok[j] = alive[j] ? ct[i] : 0x7fffffff;
-  }
-  if (m.top_p < 1.f) {
+// Top-p over the n <= kTailSurvCap top-k survivors, then the Gumbel argmax: the arithmetic of
+// resolve_candidates (sampler.cu), so both paths pick the same token with the same score.
+static __device__ __noinline__ void warp_topp_gumbel(const float* cv, const int* ct, int n, float T, float top_p, int seed,
+                                              float* y, unsigned long long* w, unsigned char* alive, int lane,
+                                              float* s_out, int* t_out) {
+#pragma unroll 1
+  for (int i = lane; i < n; i += 32) { y[i] = cv[i] / T; alive[i] = 1; }
+  __syncwarp();
+  if (top_p < 1.f) {
     float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kTailSurvRegs; ++j) mx = fmaxf(mx, y[j]);
+#pragma unroll 1
+    for (int i = lane; i < n; i += 32) mx = fmaxf(mx, y[i]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    unsigned long long w[kTailSurvRegs], above[kTailSurvRegs];
     unsigned long long z = 0;
-#pragma unroll
-    for (int j = 0; j < kTailSurvRegs; ++j) {
-      w[j] = alive[j] ? (unsigned long long)((double)expf(y[j] - mx) * 1099511627776.0) : 0ull;
-      above[j] = 0ull;
-      z += w[j];
+#pragma unroll 1
+    for (int i = lane; i < n; i += 32) {
+      const unsigned long long wi = (unsigned long long)((double)expf(y[i] - mx) * 1099511627776.0);
+      w[i] = wi;
+      z += wi;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
-    const double target = (double)m.top_p * (double)z;
-#pragma unroll
-    for (int jj = 0; jj < kTailSurvRegs; ++jj) {
-      if (jj < used) {
+    __syncwarp();
+    const double target = (double)top_p * (double)z;
+#pragma unroll 1
+    for (int i = lane; i < n; i += 32) {
+      const float yi = y[i];
+      unsigned long long above = 0;
 #pragma unroll 4
-        for (int src = 0; src < 32; ++src) {
-          const float yj = __shfl_sync(0xffffffffu, y[jj], src);
-          const unsigned long long wj = __shfl_sync(0xffffffffu, w[jj], src);
-#pragma unroll
-          for (int j = 0; j < kTailSurvRegs; ++j)
-            if (yj > y[j]) above[j] += wj;
-        }
-      }
+      for (int j = 0; j < n; ++j)
+        if (y[j] > yi) above += w[j];
+      if (!((double)above < target)) alive[i] = 0;
     }
-#pragma unroll
-    for (int j = 0; j < kTailSurvRegs; ++j)
-      if (alive[j] && !((double)above[j] < target)) alive[j] = false;
+    __syncwarp();
   }
-  s = -INFINITY;
-  t = 0x7fffffff;
-#pragma unroll
-  for (int j = 0; j < kTailSurvRegs; ++j) {
-    if (j < used && alive[j]) {
-      const float sc = y[j] + gumbel_noise(m.seed, (uint32_t)tok[j]);
-      if (better(sc, tok[j], s, t)) { s = sc; t = tok[j]; }
-    }
+  float s = -INFINITY;
+  int t = 0x7fffffff;
+#pragma unroll 1
+  for (int i = lane; i < n; i += 32) {
+    if (!alive[i]) continue;
+    const float sc = y[i] + gumbel_noise(seed, (uint32_t)ct[i]);
+    if (better(sc, ct[i], s, t)) { s = sc; t = ct[i]; }
   }
   warp_best_pair(s, t);
+  *s_out = s;
+  *t_out = t;
 }
 
 // Sharded step: exchange this rank's record of row b and merge the shards.  Whole warp; writes the
@@ -219,7 +204,9 @@ __device__ inline void tail_exchange_row(const PeerTable& pt, const RowMeta& m, 
     } else {
       __syncwarp();
       const int kept = warp_topk_inplace(mv, mt, r.total, m.top_k, lane);
-      if (kept <= kTailSurvCap) warp_topp_gumbel(mv, mt, kept, m, lane, s, t);
+      if (kept <= kTailSurvCap)
+        warp_topp_gumbel(mv, mt, kept, m.T, m.top_p, m.seed, reinterpret_cast<float*>(scratch + kTailOffY),
+                         reinterpret_cast<unsigned long long*>(scratch + kTailOffW), scratch + kTailOffAlive, lane, &s, &t);
     }
   }
   if (lane == 0) {
@@ -229,166 +216,199 @@ __device__ inline void tail_exchange_row(const PeerTable& pt, const RowMeta& m, 
   __syncwarp();
 }
 
-// One row, one warp.  Returns false when the row has to go to the full-row kernel.
-__device__ inline bool tail_resolve_row(const LmHeadParams& p, int b, uint8_t* scratch, int lane) {
-  const RowMeta m = decode_row(p.sp, b);
-  const int nsl = p.nslices;
-  const long long voff = p.sp.vocab_offset;
-  const bool exchange = p.peer.G > 0;
+// What the tail needs of the kernel's parameters (a small copy: the function below is not inlined)
+struct TailArgs {
+  SampleDev sp;
+  const float* slice_max;
+  const float* part_score;
+  const int* part_token;
+  const SliceList* lists;
+  int nslices;
+  long long* tokens;
+  float* scores;
+  uint8_t* records;
+  int single_shard;
+  unsigned long long* dbg;
+};
+
+// One row, one warp.  Returns 1 when the row is done, 0 when it has to go to the full-row kernel,
+// 2 when it is resolved as far as this shard goes and its record (survivors in cv / ct, count in
+// *nsv_out) still has to be exchanged.  `dry`: rehearsal - same code, nothing is written, no verdict.
+static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, uint8_t* scratch, int lane, bool dry, bool exchange,
+                                             int* nsv_out, float* win_s, int* win_t) {
+  const RowMeta m = decode_row(a.sp, b);
+  const int nsl = a.nslices;
+  const long long voff = a.sp.vocab_offset;
   const unsigned lt = (1u << lane) - 1u;
+  *nsv_out = 0;
   if (!(m.flags & ROW_CAND)) {
     // per-slice winners -> row winner (the same merge k_select does for these rows)
     float s = -INFINITY;
     int t = 0x7fffffff;
+#pragma unroll 4
     for (int i = lane; i < nsl; i += 32) {
-      const float s2 = __ldcg(p.part_score + (long long)b * nsl + i);
-      const int t2 = __ldcg(p.part_token + (long long)b * nsl + i);
+      const float s2 = __ldcg(a.part_score + (long long)b * nsl + i);
+      const int t2 = __ldcg(a.part_token + (long long)b * nsl + i);
       if (better(s2, t2, s, t)) { s = s2; t = t2; }
     }
     warp_best_pair(s, t);
     const long long tok = (long long)t + voff;
-    if (exchange) {
-      tail_exchange_row(p.peer, m, b, s, (int)tok, 0, 0, [](int) { return Cand{0.f, 0}; }, scratch, lane, p.tokens, p.scores);
-    } else if (lane == 0) {
-      tail_write_header(p.records, b, s, (int)tok, 0, 0);
-      if (p.tokens) p.tokens[b] = tok;
-      if (p.scores) p.scores[b] = s;
+    *win_s = s;
+    *win_t = (int)tok;
+    if (exchange) return 2;
+    if (lane == 0 && !dry) {
+      tail_write_header(a.records, b, s, (int)tok, 0, 0);
+      if (a.tokens) a.tokens[b] = tok;
+      if (a.scores) a.scores[b] = s;
     }
-    return true;
+    return 1;
   }
-  if (!p.list_v || m.top_k <= 0 || m.top_k > kTailMaxK || nsl > kTailMaxSlices) return false;
+  if (!a.lists || m.top_k <= 0 || m.top_k > kTailMaxK || nsl > kTailMaxSlices || (nsl & 3)) return 0;
 
-  uint16_t* sl = reinterpret_cast<uint16_t*>(scratch + kTailOffSlices);
-  uint32_t* st = reinterpret_cast<uint32_t*>(scratch + kTailOffStage);
+  uint16_t* qsel = reinterpret_cast<uint16_t*>(scratch + kTailOffQuads);
+  uint2* st = reinterpret_cast<uint2*>(scratch + kTailOffStage);
   float* cv = reinterpret_cast<float*>(scratch + kTailOffCv);
   int* ct = reinterpret_cast<int*>(scratch + kTailOffCt);
   const int K = m.top_k;
-  const float* lv = p.list_v + (long long)b * kListLen * nsl;  // [position][slice]
-  const int* ltok = p.list_t + (long long)b * kListM * nsl;
+  const int nq = nsl >> 2;  // CTAs: four consecutive slices each
+  const float4* heads4 = reinterpret_cast<const float4*>(a.slice_max + (long long)b * nsl);
+  const uint4* recs = reinterpret_cast<const uint4*>(a.lists + (long long)b * nsl);
 
-  // 1. slice heads (= list position 0) -> keys in registers, one batch of independent loads
-  uint32_t hk[kTailHeadRegs];
-  const int hused = (nsl + 31) >> 5;
+  // 1. trip one: the slice maxima, one 16-byte load per CTA; key of a CTA = its largest
+  uint32_t qk[kTailQuadRegs];
   int nfin = 0;
 #pragma unroll
-  for (int j = 0; j < kTailHeadRegs; ++j) {
-    float v = -INFINITY;
-    if (j < hused && j * 32 + lane < nsl) v = __ldcg(lv + j * 32 + lane);
-    hk[j] = h16_key(v);
-    nfin += (hk[j] >= kKeyLowestFinite);
+  for (int j = 0; j < kTailQuadRegs; ++j) {
+    float4 h = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    if (j * 32 + lane < nq) h = __ldcg(heads4 + j * 32 + lane);
+    qk[j] = h16_key(fmaxf(fmaxf(h.x, h.y), fmaxf(h.z, h.w)));
+    nfin += (qk[j] >= kKeyLowestFinite);
   }
   nfin = __reduce_add_sync(0xffffffffu, nfin);
-  if (b == 0 && lane == 0 && p.dbg) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.dbg[(size_t)blockIdx.x * 16 + 5] = t_; }
-  // 2. tau0 = K-th largest head: K slices hold a value >= it, so the K-th largest logit is >= it
+  // 2. tau0 = K-th largest CTA maximum: K distinct logits are >= it, so the K-th largest logit is
+  //    (bisection on the 16 key bits; every round is kTailQuadRegs compares and one warp vote)
   uint32_t tau0 = kKeyLowestFinite;
-  if (nfin >= K) tau0 = warp_kth_largest_reg(hk, hused, K, 15, 0);
-  if (tau0 < kKeyLowestFinite) tau0 = kKeyLowestFinite;
-  if (b == 0 && lane == 0 && p.dbg) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.dbg[(size_t)blockIdx.x * 16 + 6] = t_; }
-  // 3. the slices that can hold a logit >= tau0
-  int ns = 0;
-#pragma unroll
-  for (int j = 0; j < kTailHeadRegs; ++j) {
-    if (j < hused) {
-      const bool hit = hk[j] >= tau0;  // unused slots hold key(-inf)
-      const unsigned mask = __ballot_sync(0xffffffffu, hit);
-      const int pos = ns + __popc(mask & lt);
-      if (hit && pos < kTailSliceCap) sl[pos] = (uint16_t)(j * 32 + lane);
-      ns += __popc(mask);
-    }
-  }
-  if (ns > kTailSliceCap) return false;
-  __syncwarp();
-  if (b == 0 && lane == 0 && p.dbg) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.dbg[(size_t)blockIdx.x * 16 + 7] = t_; }
-  // 4. their list entries, eight independent loads per lane at a time: values >= tau0 are staged as
-  //    (key, entry index = slice slot * kListLen + position); witnesses are folded to a maximum
-  const int nent = ns * kListLen;
-  int ne = 0;
-  uint32_t wkey = 0;
+  if (nfin >= K) {
+    uint32_t prefix = 0;
 #pragma unroll 1
-  for (int base = 0; base < nent; base += 256) {
-    float v[8];
+    for (int bit = 15; bit >= 0; --bit) {
+      const uint32_t cand = prefix | (1u << bit);
+      int c = 0;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const int i = base + r * 32 + lane;
-      v[r] = -INFINITY;
-      if (i < nent) v[r] = __ldcg(lv + (i % kListLen) * nsl + (int)sl[i / kListLen]);
+      for (int j = 0; j < kTailQuadRegs; ++j) c += (qk[j] >= cand);
+      if (__reduce_add_sync(0xffffffffu, c) >= K) prefix = cand;
     }
+    tau0 = prefix;
+  }
+  if (tau0 < kKeyLowestFinite) tau0 = kKeyLowestFinite;
+  // 3. the CTAs that can hold a logit >= tau0
+  int nsel = 0;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
+  for (int j = 0; j < kTailQuadRegs; ++j) {
+    const bool hit = qk[j] >= tau0;  // unused slots hold key(-inf)
+    const unsigned mask = __ballot_sync(0xffffffffu, hit);
+    const int pos = nsel + __popc(mask & lt);
+    if (hit && pos < kTailQuadCap) qsel[pos] = (uint16_t)(j * 32 + lane);
+    nsel += __popc(mask);
+  }
+  if (nsel > kTailQuadCap) return 0;
+  __syncwarp();
+  // 4. trip two: the list records of their slices (two 16-byte loads each, up to kTailRecRegs per lane
+  //    in flight at once); every listed value >= tau0 is staged as (key, token); witnesses are folded
+  //    to a maximum
+  const int nrec = nsel * 4;
+  uint32_t wkey = 0;
+  int ne = 0;
+#pragma unroll 1
+  for (int base = 0; base < nrec; base += kTailRecRegs * 32) {
+    uint4 rt[kTailRecRegs], rv[kTailRecRegs];
+#pragma unroll
+    for (int r = 0; r < kTailRecRegs; ++r) {
       const int i = base + r * 32 + lane;
-      if (base + r * 32 < nent) {  // uniform
-        const uint32_t k = h16_key(v[r]);
-        const bool wit = i < nent && (i % kListLen) == kListM;
-        if (wit) wkey = max(wkey, k);
-        const bool take = i < nent && !wit && k >= tau0;
-        const unsigned mask = __ballot_sync(0xffffffffu, take);
-        if (take) st[ne + __popc(mask & lt)] = (k << 16) | (uint32_t)i;
-        ne += __popc(mask);
+      rt[r] = make_uint4(0, 0, 0, 0);
+      rv[r] = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0);  // five times -inf
+      if (i < nrec) {
+        const int slice = (int)qsel[i >> 2] * 4 + (i & 3);
+        rt[r] = __ldcg(recs + 2 * slice);
+        rv[r] = __ldcg(recs + 2 * slice + 1);
       }
     }
+    int mine_n = 0;
+#pragma unroll
+    for (int r = 0; r < kTailRecRegs; ++r) {
+      const uint32_t k0 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].x & 0xffffu))));
+      const uint32_t k1 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].x >> 16))));
+      const uint32_t k2 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].y & 0xffffu))));
+      const uint32_t k3 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].y >> 16))));
+      const uint32_t kw = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].z & 0xffffu))));
+      if (k0 >= tau0) wkey = max(wkey, kw);  // a slice whose maximum is below tau0 hides nothing that matters
+      mine_n += (k0 >= tau0) + (k1 >= tau0) + (k2 >= tau0) + (k3 >= tau0);
+      rv[r] = make_uint4(k0, k1, k2, k3);    // keep the keys
+    }
+    int incl = mine_n;  // prefix over the lanes: where this lane's staged entries go
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t2 = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t2;
+    }
+    const int batch = __shfl_sync(0xffffffffu, incl, 31);
+    if (ne + batch > kTailStageCap) return 0;
+    int wpos = ne + incl - mine_n;
+#pragma unroll
+    for (int r = 0; r < kTailRecRegs; ++r) {
+      if (rv[r].x >= tau0) st[wpos++] = make_uint2(rv[r].x, rt[r].x);
+      if (rv[r].y >= tau0) st[wpos++] = make_uint2(rv[r].y, rt[r].y);
+      if (rv[r].z >= tau0) st[wpos++] = make_uint2(rv[r].z, rt[r].z);
+      if (rv[r].w >= tau0) st[wpos++] = make_uint2(rv[r].w, rt[r].w);
+    }
+    ne += batch;
   }
   wkey = __reduce_max_sync(0xffffffffu, wkey);
   __syncwarp();
-  if (b == 0 && lane == 0 && p.dbg) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.dbg[(size_t)blockIdx.x * 16 + 8] = t_; }
   // 5. t_k: the K-th largest staged value (every staged value survives when fewer than K exist)
-  uint32_t sk[kTailStageRegs];
-  const int sused = (ne + 31) >> 5;
-#pragma unroll
-  for (int j = 0; j < kTailStageRegs; ++j) {
-    sk[j] = 0;
-    if (j < sused && j * 32 + lane < ne) sk[j] = st[j * 32 + lane];
-  }
   uint32_t tk = kKeyLowestFinite;
-  if (ne >= K) {
-    uint32_t kk[kTailStageRegs];
-#pragma unroll
-    for (int j = 0; j < kTailStageRegs; ++j) kk[j] = sk[j] >> 16;
-    tk = warp_kth_largest_reg(kk, sused, K, 15, 0);
-  }
-  if (b == 0 && lane == 0 && p.dbg) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.dbg[(size_t)blockIdx.x * 16 + 9] = t_; }
-  // 6. the proof: no slice we looked at hides a value >= t_k (slices we skipped have head < tau0 <= t_k)
-  if (wkey >= tk) return false;
+  if (ne >= K) tk = warp_kth_largest_key([&](int i) { return st[i].x; }, ne, K, 15, 0, lane);
+  // 6. the proof: no slice we looked at hides a value >= t_k (the others have maximum < tau0 <= t_k)
+  if (wkey >= tk && !dry) return 0;
   // 7. survivors (>= t_k, ties kept), with their GLOBAL token ids
   int nsv = 0;
-#pragma unroll
-  for (int j = 0; j < kTailStageRegs; ++j) {
-    if (j < sused) {
-      const bool keep = (sk[j] >> 16) >= tk && sk[j] != 0;
-      const unsigned mask = __ballot_sync(0xffffffffu, keep);
-      const int pos = nsv + __popc(mask & lt);
-      if (keep && pos < kTailSurvCap) {
-        const uint32_t e = sk[j] & 0xffffu;
-        cv[pos] = h16_key_to_float(sk[j] >> 16);
-        ct[pos] = (int)((long long)__ldcg(ltok + (e % kListLen) * nsl + (int)sl[e / kListLen]) + voff);
-      }
-      nsv += __popc(mask);
+#pragma unroll 1
+  for (int i0 = 0; i0 < ne; i0 += 32) {
+    const int i = i0 + lane;
+    const uint2 e = i < ne ? st[i] : make_uint2(0u, 0u);
+    const bool keep = i < ne && e.x >= tk;
+    const unsigned mask = __ballot_sync(0xffffffffu, keep);
+    const int pos = nsv + __popc(mask & lt);
+    if (keep && pos < kTailSurvCap) {
+      cv[pos] = h16_key_to_float(e.x);
+      ct[pos] = (int)((long long)(int)e.y + voff);
     }
+    nsv += __popc(mask);
   }
-  if (nsv > kTailSurvCap) return false;
+  if (nsv > kTailSurvCap) {
+    if (!dry) return 0;
+    nsv = kTailSurvCap;
+  }
   __syncwarp();
-  if (exchange) {
-    if (nsv > VQK_RECORD_CAP) return false;  // the full-row kernel reports the overflow
-    tail_exchange_row(p.peer, m, b, -INFINITY, -1, nsv, 0, [&](int i) { return Cand{cv[i], ct[i]}; }, scratch, lane,
-                      p.tokens, p.scores);
-    return true;
-  }
-  if (p.records) {  // shard record: the local top-k survivors; top-p needs the union of the shards
-    Cand* out = reinterpret_cast<Cand*>(p.records + (size_t)b * VQK_RECORD_BYTES + sizeof(RecordHeader));
+  *nsv_out = nsv;
+  if (exchange) return nsv > VQK_RECORD_CAP ? 0 : 2;  // (the full-row kernel reports an overflowing record)
+  if (a.records && !dry) {  // shard record: the local top-k survivors; top-p needs the union of the shards
+    Cand* out = reinterpret_cast<Cand*>(a.records + (size_t)b * VQK_RECORD_BYTES + sizeof(RecordHeader));
     for (int i = lane; i < nsv && i < VQK_RECORD_CAP; i += 32) out[i] = Cand{cv[i], ct[i]};
     if (lane == 0)
-      tail_write_header(p.records, b, -INFINITY, -1, min(nsv, VQK_RECORD_CAP), nsv > VQK_RECORD_CAP ? VQK_RECORD_FLAG_OVERFLOW : 0);
+      tail_write_header(a.records, b, -INFINITY, -1, min(nsv, VQK_RECORD_CAP), nsv > VQK_RECORD_CAP ? VQK_RECORD_FLAG_OVERFLOW : 0);
   }
-  if (!p.single_shard) return true;
-  if (b == 0 && lane == 0 && p.dbg) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.dbg[(size_t)blockIdx.x * 16 + 10] = t_; }
+  if (!a.single_shard) return 1;
   // 8. top-p over the survivors, then the Gumbel argmax
   float s;
   int t;
-  warp_topp_gumbel(cv, ct, nsv, m, lane, s, t);
-  if (lane == 0) {
-    if (p.tokens) p.tokens[b] = t;
-    if (p.scores) p.scores[b] = s;
+  warp_topp_gumbel(cv, ct, nsv, m.T, m.top_p, m.seed, reinterpret_cast<float*>(scratch + kTailOffY),
+                   reinterpret_cast<unsigned long long*>(scratch + kTailOffW), scratch + kTailOffAlive, lane, &s, &t);
+  if (lane == 0 && !dry) {
+    if (a.tokens) a.tokens[b] = t;
+    if (a.scores) a.scores[b] = s;
   }
-  return true;
+  return 1;
 }
 
 // Called by every thread of every CTA once its slice results are written.  `scratch` is shared
@@ -407,9 +427,27 @@ __device__ inline void lm_head_tail(const LmHeadParams& p, uint8_t* scratch, siz
   nw = min(nw, (int)(scratch_bytes / kTailWarpBytes));
   if (warp < nw) {
     uint8_t* mine = scratch + (size_t)warp * kTailWarpBytes;
+    TailArgs a;
+    a.sp = p.sp; a.slice_max = p.slice_max; a.part_score = p.part_score; a.part_token = p.part_token;
+    a.lists = p.lists; a.nslices = p.nslices; a.tokens = p.tokens; a.scores = p.scores;
+    a.records = p.records; a.single_shard = p.single_shard; a.dbg = p.dbg;
+    const bool exchange = p.peer.G > 0;
     for (int b = warp; b < p.B; b += nw) {
-      const bool done = p.fuse_tail == 1 && tail_resolve_row(p, b, mine, lane);  // 2: every row to the full-row kernel (A/B runs)
-      if (lane == 0) p.row_flag[b] = done ? 0 : 1;
+      int nsv = 0, wt = 0;
+      float ws = 0.f;
+      int r = 0;
+      if (p.fuse_tail == 1) r = tail_resolve_row(a, b, mine, lane, false, exchange, &nsv, &ws, &wt);  // 2: A/B runs, every row to the full-row kernel
+      if (r == 2) {
+        const RowMeta m = decode_row(p.sp, b);
+        const float* cv = reinterpret_cast<const float*>(mine + kTailOffCv);
+        const int* ct = reinterpret_cast<const int*>(mine + kTailOffCt);
+        if (m.flags & ROW_CAND)
+          tail_exchange_row(p.peer, m, b, -INFINITY, -1, nsv, 0, [&](int i) { return Cand{cv[i], ct[i]}; }, mine, lane, p.tokens, p.scores);
+        else
+          tail_exchange_row(p.peer, m, b, ws, wt, 0, 0, [](int) { return Cand{0.f, 0}; }, mine, lane, p.tokens, p.scores);
+        r = 1;
+      }
+      if (lane == 0) p.row_flag[b] = r ? 0 : 1;
       __syncwarp();
     }
   }

@@ -160,7 +160,10 @@ __device__ __forceinline__ float key_to_float(int k) {
 // NI: independent MMA pipelines ("lanes") in the CTA.  The CTA's n-th tile is computed by lane
 // n % NI into that lane's accumulator (n / NI) % 2, at TMEM columns ((n % NI) * 2 + buffer) * BN,
 // and announced / released through tfull / tempty at the same index.
-template <int EPI, int BN, int NI = 1>
+// KSPLIT: the NI pipelines work on the SAME tile, each on its share of K, into its own accumulator
+// (buffer l * 2 + (n & 1) for the CTA's n-th tile); the epilogue waits for all of them and adds the
+// partial sums in pipeline order.
+template <int EPI, int BN, int NI = 1, bool KSPLIT = false>
 __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, int lane, uint32_t tmem_base,
                                               uint64_t* tfull, uint64_t* tempty, volatile int* abort_flag,
                                               const RowMeta* meta, int* sstate, const TileSched& sched, Cand* qlists,
@@ -178,7 +181,7 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
     // decode-sized batches: the kListLen largest logits of every top-k column in this warp's rows
     // (`qlists`: [4 warps][kTailMaxBatch][kListLen] entries of shared memory; when it is borrowed from a
     // buffer the kernel's start-up still reads, `qlists_free` is the barrier that says it is done)
-    const bool use_lists = p.list_v != nullptr && qlists != nullptr;
+    const bool use_lists = p.lists != nullptr && qlists != nullptr;
     Cand* ql = qlists + (size_t)q * kTailMaxBatch * kListLen;
     if (use_lists) {
       if (qlists_free) mbar_wait_warp(qlists_free, 0, abort_flag);
@@ -188,11 +191,12 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
     float xs_w8a8 = 1.f;
     if constexpr (INT8) xs_w8a8 = *reinterpret_cast<const float*>(p.xscale);
     const int nchunk = (B + 15) / 16;
+    const bool post_ops = p.soft_cap > 0.f || p.out_scale != 1.f;
 
     const int mytiles = sched.count();
     for (int tcount = 0; tcount < mytiles; ++tcount) {
-      const int buf = (tcount % NI) * 2 + ((tcount / NI) & 1);
-      const uint32_t tph = (uint32_t)((tcount / NI) >> 1) & 1u;
+      const int buf = KSPLIT ? (tcount & 1) : (tcount % NI) * 2 + ((tcount / NI) & 1);
+      const uint32_t tph = KSPLIT ? (uint32_t)(tcount >> 1) & 1u : (uint32_t)((tcount / NI) >> 1) & 1u;
       const int tile_row0 = sched.row0(tcount), tile_lim = sched.limit(tcount);
       const int row = tile_row0 + q * 32 + lane;
       const bool rok = row < tile_lim;
@@ -202,12 +206,29 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
       if constexpr (EPI == 0) rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[rowc]);
       const float bias = p.bias ? __half2float(p.bias[rowc]) : 0.f;
       if (!mbar_wait_warp(&tfull[buf], tph, abort_flag)) break;
+      if constexpr (KSPLIT) {
+        bool all = true;
+#pragma unroll
+        for (int l = 1; l < NI; ++l) all = all && mbar_wait_warp(&tfull[l * 2 + buf], tph, abort_flag);
+        if (!all) break;
+      }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
       for (int ch = 0; ch < nchunk; ++ch) {
         const int c0 = ch * 16;
         uint32_t r[16];
         tmem_ld16(taddr + (uint32_t)c0, r);
+        if constexpr (KSPLIT) {
+          static_assert(!KSPLIT || EPI != 1, "partial sums are added as fp32");
+#pragma unroll
+          for (int l = 1; l < NI; ++l) {
+            uint32_t r2[16];
+            tmem_ld16(taddr + (uint32_t)(l * 2 * BN + c0), r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+          }
+        }
         // which of the 16 columns take the candidate path / exist at all
         int myflags = 0;
         if (lane < 16 && c0 + lane < B && p.do_sample) myflags = meta[c0 + lane].flags | 0x100;
@@ -217,7 +238,7 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
         __half* cp = p.cand_logits + (long long)c0 * p.ld_cand + rowc;
         int mine_max = ordered_key(-INFINITY);
         tmem_ld_wait();
-        if (!p.bias && !use_lists && c0 + 16 <= B && (!p.do_sample || (candmask & 0xffffu) == 0xffffu)) {
+        if (!p.bias && !post_ops && !use_lists && c0 + 16 <= B && (!p.do_sample || (candmask & 0xffffu) == 0xffffu)) {
           // Fast path (all 16 columns exist and take the candidate path, or no sampling at all):
           // packed fp16 conversion, one store per column, and the 32-row maximum of every column
           // by a half2 butterfly over the warp instead of sixteen warp reductions.
@@ -289,6 +310,7 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
           else v = __uint_as_float(r[j]) * rs;
           __half h = __float2half_rn(v);
           if (p.bias) h = __float2half_rn(__half2float(h) + bias);
+          h = logit_post_ops(h, p.soft_cap, p.out_scale);
           if (c0 + j < B) {  // warp-uniform
             if (lp && rok) lp[(long long)j * p.ld_logits] = h;
             if (candmask & (1u << j)) {
@@ -332,7 +354,13 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[buf]);
+      if (lane == 0) {
+        mbar_arrive(&tempty[buf]);
+        if constexpr (KSPLIT) {
+#pragma unroll
+          for (int l = 1; l < NI; ++l) mbar_arrive(&tempty[l * 2 + buf]);
+        }
+      }
     }
     __syncwarp();
     if (p.do_sample) {
@@ -344,10 +372,15 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
         p.part_token[o] = st_tok[b];
       }
       if (use_lists)
-        for (int i = lane; i < B * kListLen; i += 32) {
-          const int b = i / kListLen, pos = i % kListLen;
-          p.list_v[((long long)b * kListLen + pos) * p.nslices + slice] = ql[i].v;
-          if (pos < kListM) p.list_t[((long long)b * kListM + pos) * p.nslices + slice] = ql[i].t;
+        for (int b = lane; b < B; b += 32) {
+          SliceList rec;
+#pragma unroll
+          for (int i = 0; i < kListLen; ++i) {
+            rec.v[i] = __float2half_rn(ql[b * kListLen + i].v);
+            if (i < kListM) rec.t[i] = ql[b * kListLen + i].t;
+          }
+          rec.pad[0] = rec.pad[1] = rec.pad[2] = __float2half_rn(0.f);
+          p.lists[(long long)b * p.nslices + slice] = rec;
         }
     }
 }

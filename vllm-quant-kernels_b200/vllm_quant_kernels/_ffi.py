@@ -28,7 +28,7 @@ SYMBOLS = (
     "vqk_version", "vqk_strerror", "vqk_last_cuda_error", "vqk_device_error", "vqk_device_error_clear",
     "vqk_quantize_weight", "vqk_quantize_act",
     "vqk_lm_head_create", "vqk_lm_head_destroy", "vqk_lm_head_workspace_bytes", "vqk_lm_head_forward",
-    "vqk_lm_head_set_kernel_events", "vqk_lm_head_set_debug_times",
+    "vqk_lm_head_set_kernel_events", "vqk_lm_head_set_debug_times", "vqk_lm_head_set_post_ops",
     "vqk_sample_workspace_bytes", "vqk_sample", "vqk_sample_static", "vqk_sample_finalize", "vqk_topk_threshold",
     "vqk_comm_unique_id", "vqk_comm_create", "vqk_comm_allgather", "vqk_comm_destroy",
     "vqk_peer_create", "vqk_peer_connect", "vqk_peer_connect_pointers", "vqk_peer_local_buffer",
@@ -79,6 +79,7 @@ def lib() -> ctypes.CDLL:
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     L.vqk_lm_head_set_kernel_events.argtypes = [c_void_p, c_void_p, c_void_p]
     L.vqk_lm_head_set_debug_times.argtypes = [c_void_p, c_void_p]
+    L.vqk_lm_head_set_post_ops.argtypes = [c_void_p, c_float, c_float]
     L.vqk_sample_workspace_bytes.restype = c_int64
     L.vqk_sample_workspace_bytes.argtypes = [c_int64, c_int64]
     L.vqk_sample.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int64, POINTER(SampleParams), c_void_p, c_void_p,

@@ -200,6 +200,11 @@ class LMHeadShard:
         b = None if stop is None else stop.cuda_event
         _ffi.check(_ffi.lib().vqk_lm_head_set_kernel_events(self._h, a, b))
 
+    def set_post_ops(self, soft_cap: Optional[float] = None, scale: float = 1.0) -> None:
+        """vLLM's logits post-ops (soft cap, then scale) applied in the lm_head epilogue of every
+        following call on this shard, with upstream's fp16 roundings; (None, 1.0) switches them off."""
+        _ffi.check(_ffi.lib().vqk_lm_head_set_post_ops(self._h, float(soft_cap) if soft_cap else 0.0, float(scale)))
+
     def _x2d(self, x: torch.Tensor) -> torch.Tensor:
         _require_cuda(x, "hidden_states")
         x = x.reshape(-1, self.H)

@@ -23,7 +23,7 @@ from vllm.model_executor.layers.vocab_parallel_embedding import (
     VocabParallelEmbedding,
 )
 
-from . import _lmhead
+from . import _checkpoint, _lmhead
 from ._kernels import MXFP4_GROUP_SIZE, MXFP8_GROUP_SIZE
 
 _QUANT_ATTRS = ("_mxfp4_w", "_mxfp8_w", "_fp8_w", "_w8a8_w", "_int8_w")
@@ -61,6 +61,25 @@ class QuantizedLogitsProcessor(LogitsProcessor):
     """vLLM LogitsProcessor with a quantized lm_head matmul (reference: _quant.py:108-643)."""
 
     _VOCAB_THRESHOLD = 100_000
+
+    def forward(self, lm_head, hidden_states, embedding_bias=None):
+        """Upstream's forward (vllm logits_processor.py:54-73) with its post-ops - soft cap and scale,
+        three to four extra passes over [B, V] there - folded into the lm_head epilogue when the
+        quantized path runs.  Same values: the epilogue rounds to fp16 where upstream's tensor ops do."""
+        if getattr(self, "logits_as_input", False):
+            return super().forward(lm_head, hidden_states, embedding_bias)
+        if not hasattr(self, "_int8_initialized"):
+            self._int8_initialized = True
+            self._init_int8(lm_head)
+        shard = getattr(lm_head, "_vqk_shard", None)
+        soft_cap, scale = getattr(self, "soft_cap", None), getattr(self, "scale", 1.0)
+        if shard is None or (soft_cap is None and scale == 1.0):
+            return super().forward(lm_head, hidden_states, embedding_bias)
+        shard.set_post_ops(soft_cap, scale)
+        try:
+            return self._get_logits(hidden_states, lm_head, embedding_bias)
+        finally:
+            shard.set_post_ops(None, 1.0)   # direct _quantized_forward calls keep returning raw logits
 
     def _get_logits(
         self,
@@ -144,32 +163,42 @@ class QuantizedLogitsProcessor(LogitsProcessor):
     def _banner(_sys, text):
         print(f"[vllm-quant-kernels] lm_head quantized: {text}", file=_sys.stderr, flush=True)
 
+    @staticmethod
+    def _quantize(mode, w):
+        """Quantized codes and scales of `w`: computed, or read back from the directory
+        `VLLM_QUANT_LMHEAD_CACHE` names when it holds them for this very weight (_checkpoint.py)."""
+        q, s, how = _checkpoint.quantize_or_load(mode, w, _lmhead.quantize_weight)
+        if how != "quantized":
+            print(f"[vllm-quant-kernels] lm_head {mode}: {how} ({os.environ.get('VLLM_QUANT_LMHEAD_CACHE')})",
+                  file=sys.stderr, flush=True)
+        return q, s
+
     def _init_int8_weights(self, lm_head, w, _sys, is_thor: bool = True) -> None:
         """Per-row INT8 + fp16 scale (reference: _quant.py:245-273).  The original weight
         is kept: with tied embeddings it is the embedding table."""
         lm_head._int8_use_thor = True
-        lm_head._int8_w, lm_head._int8_scales = _lmhead.quantize_weight("int8", w)
+        lm_head._int8_w, lm_head._int8_scales = self._quantize("int8", w)
         lm_head._vqk_shard = _lmhead.LMHeadShard("int8", lm_head._int8_w, lm_head._int8_scales)
         saved_mb = w.numel() * w.element_size() // 1024 // 1024
         self._banner(_sys, f"fp16 {w.shape[0]}×{w.shape[1]} → int8 (saved {saved_mb} MB, kernel=b200/int8)")
 
     def _init_w8a8(self, lm_head, w, _sys) -> None:
         """Per-row INT8 + fp32 scale; activations per-tensor INT8 at run time (reference: _quant.py:278-304)."""
-        lm_head._w8a8_w, lm_head._w8a8_scales = _lmhead.quantize_weight("w8a8", w)
+        lm_head._w8a8_w, lm_head._w8a8_scales = self._quantize("w8a8", w)
         lm_head._vqk_shard = _lmhead.LMHeadShard("w8a8", lm_head._w8a8_w, lm_head._w8a8_scales)
         saved_mb = w.numel() * w.element_size() // 1024 // 1024
         self._banner(_sys, f"fp16 {w.shape[0]}×{w.shape[1]} → int8 w8a8 (saved {saved_mb} MB, kernel=b200/w8a8)")
 
     def _init_fp8(self, lm_head, w, _sys) -> None:
         """Per-row FP8 e4m3 stored as an int8 view + fp16 scale (reference: _quant.py:306-327)."""
-        lm_head._fp8_w, lm_head._fp8_scales = _lmhead.quantize_weight("fp8", w)
+        lm_head._fp8_w, lm_head._fp8_scales = self._quantize("fp8", w)
         lm_head._vqk_shard = _lmhead.LMHeadShard("fp8", lm_head._fp8_w, lm_head._fp8_scales)
         saved_mb = w.numel() * w.element_size() // 1024 // 1024
         self._banner(_sys, f"fp16 {w.shape[0]}×{w.shape[1]} → fp8e4m3 (saved {saved_mb} MB, kernel=b200/fp8)")
 
     def _init_mxfp8(self, lm_head, w, _sys) -> None:
         """e4m3 + E8M0 per 32 (reference: _quant.py:329-352)."""
-        lm_head._mxfp8_w, lm_head._mxfp8_w_scales = _quantize_to_mxfp8(w)
+        lm_head._mxfp8_w, lm_head._mxfp8_w_scales = self._quantize("mxfp8", w)
         lm_head._vqk_shard = _lmhead.LMHeadShard("mxfp8", lm_head._mxfp8_w, lm_head._mxfp8_w_scales)
         saved_mb = w.numel() * w.element_size() // 1024 // 1024
         scale_mb = lm_head._mxfp8_w_scales.numel() // 1024 // 1024
@@ -178,7 +207,7 @@ class QuantizedLogitsProcessor(LogitsProcessor):
 
     def _init_mxfp4(self, lm_head, w, _sys) -> None:
         """E2M1 packed two per byte + E8M0 per 32; W4A8 at run time (reference: _quant.py:354-380)."""
-        lm_head._mxfp4_w, lm_head._mxfp4_w_scales = _quantize_to_mxfp4(w)
+        lm_head._mxfp4_w, lm_head._mxfp4_w_scales = self._quantize("mxfp4", w.detach())
         lm_head._mxfp4_K = int(w.shape[1])
         lm_head._vqk_shard = _lmhead.LMHeadShard("mxfp4", lm_head._mxfp4_w, lm_head._mxfp4_w_scales, lm_head._mxfp4_K)
         orig_mb = w.numel() * w.element_size() // 1024 // 1024
@@ -257,4 +286,9 @@ class QuantizedLogitsProcessor(LogitsProcessor):
             sh = fs
         if embedding_bias is not None and embedding_bias.shape[-1] > sh.V:
             embedding_bias = embedding_bias[..., :sh.V]
-        return sh.sample(hidden_states, sampling_args, embedding_bias)
+        # the distribution vLLM samples from is the one after its post-ops (soft cap, scale)
+        sh.set_post_ops(getattr(self, "soft_cap", None), getattr(self, "scale", 1.0))
+        try:
+            return sh.sample(hidden_states, sampling_args, embedding_bias)
+        finally:
+            sh.set_post_ops(None, 1.0)

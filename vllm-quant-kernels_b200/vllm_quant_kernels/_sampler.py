@@ -61,6 +61,49 @@ def _make_seeds(batch_size: int, device: torch.device) -> torch.Tensor:
     return torch.randint(low=0, high=2**31 - 1, size=(batch_size,), dtype=torch.int32, device=device)
 
 
+def try_fused_step(logits_processor, lm_head, hidden_states: torch.Tensor, sampling_metadata: "SamplingMetadata",
+                   embedding_bias: "torch.Tensor | None" = None, seeds: "torch.Tensor | None" = None,
+                   logprobs_mode: str = "raw_logprobs") -> "torch.Tensor | None":
+    """The whole decode tail in one call: lm_head and sampler fused, logits never materialised.
+
+    vLLM's runner calls `model.compute_logits(hidden)` and `sampler(logits, metadata)` one after the
+    other; the two plugin hooks can only speed each up.  A runner that owns both calls can ask this
+    function first: it returns the sampled token ids (int64 [B]) when the batch is on the fused
+    path, or None, in which case the runner goes on with compute_logits + sampler as before.
+
+    On the fused path: the quantized lm_head of `logits_processor` (a QuantizedLogitsProcessor),
+    the fast-path predicate of the sampler hook, no logprobs of any kind (they need the logits), no
+    penalties and no speculative tokens.  Soft cap, scale, bias and the vocabulary-padding trim are
+    applied like upstream does before sampling."""
+    sm = sampling_metadata
+    if not hidden_states.is_cuda or not hasattr(logits_processor, "sample_fused"):
+        return None
+    if not _fast_path_ok(sm):
+        return None
+    if sm.max_num_logprobs is not None or sm.logprob_token_ids:
+        return None
+    if not getattr(sm, "no_penalties", True) or getattr(sm, "spec_token_ids", None):
+        return None
+    if getattr(lm_head, "_vqk_shard", None) is None and hasattr(logits_processor, "_int8_initialized"):
+        return None                                   # this lm_head is not quantized: upstream path
+    B = hidden_states.reshape(-1, hidden_states.shape[-1]).shape[0]
+    if sm.all_greedy:
+        sp = SamplingArgs()
+    else:
+        assert sm.temperature is not None
+        sp = SamplingArgs(
+            temperature=sm.temperature.to(torch.float32).contiguous(),
+            seeds=_make_seeds(B, hidden_states.device) if seeds is None else seeds,
+            top_k=None if sm.top_k is None else sm.top_k.to(torch.int32).contiguous(),
+            top_p=None if sm.top_p is None else sm.top_p.to(torch.float32).contiguous(),
+        )
+    try:
+        tokens, _ = logits_processor.sample_fused(hidden_states, lm_head, sp, embedding_bias)
+    except RuntimeError:
+        return None                                   # not quantized / tensor parallel: upstream path
+    return tokens
+
+
 def install_fused_sampler() -> None:
     """Monkey-patch vllm.v1.sample.sampler.Sampler with the fused variant.  Must run
     before `vllm.v1.worker.gpu_model_runner` imports Sampler by name
