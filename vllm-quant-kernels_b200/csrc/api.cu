@@ -3,6 +3,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
 #include <new>
 
 #include "lm_head.cuh"
@@ -87,10 +88,12 @@ struct LmHeadWs {
 constexpr int kTicketSlots = 256;
 static __device__ unsigned int g_tickets[kTicketSlots];
 static unsigned int* g_tickets_ptr[64];
+static std::mutex g_symbol_mu;  // the once-per-device address look-ups may come from several host threads
 static int ticket_base(unsigned int** out) {
   int dev = 0;
   VQK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
+  std::lock_guard<std::mutex> lock(g_symbol_mu);
   if (!g_tickets_ptr[dev]) {
     void* ptr = nullptr;
     VQK_CUDA(cudaGetSymbolAddress(&ptr, g_tickets));
@@ -107,6 +110,7 @@ static int peer_error_word(int** out) {
   int dev = 0;
   VQK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
+  std::lock_guard<std::mutex> lock(g_symbol_mu);
   if (!g_peer_error_ptr[dev]) {
     void* ptr = nullptr;
     VQK_CUDA(cudaGetSymbolAddress(&ptr, g_peer_error));
@@ -306,12 +310,17 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   if (sp) sd = to_dev(sp);
   // Decode-sized batches: the lm_head kernel's last CTA resolves the rows itself (tail.cuh); the
   // full-row kernel behind it only picks up rows the tail flagged.
+  // The streaming kernel always, the tensor-core kernels when the step is sharded over peer memory
+  // (one kernel instead of three) - on one GPU their tail ran slower than the full-row kernel it
+  // replaces.  VQK_TAIL_MODE (A/B runs): 0 = never, 2 = the tail hands every row to the full-row
+  // kernel, 3 = every kernel.
   static const int tail_mode = [] {
-    const char* e = getenv("VQK_TAIL_MODE");  // A/B runs: 0 = no tail, 2 = tail sends every row to the full-row kernel
+    const char* e = getenv("VQK_TAIL_MODE");
     const int v = e ? atoi(e) : 1;
-    return v >= 0 && v <= 2 ? v : 1;
+    return v >= 0 && v <= 3 ? v : 1;
   }();
-  const bool fuse_tail = tail_mode && sp && B <= kTailMaxBatch && B <= maxcols && nslices <= 1024;
+  const bool tail_here = tail_mode == 3 || !use_umma || peer != nullptr;
+  const bool fuse_tail = tail_mode && tail_here && sp && B <= kTailMaxBatch && B <= maxcols && nslices <= 1024;
   unsigned int* tickets = nullptr;
   int* error_word = nullptr;
   if (fuse_tail) {
@@ -362,7 +371,7 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
         p.ld_cand = ws.ld_cand;
       }
       if (fuse_tail) {
-        p.fuse_tail = tail_mode;
+        p.fuse_tail = tail_mode == 2 ? 2 : 1;
         p.lists = ws.lists;
         p.ticket = tickets + h->ticket_slot;
         p.error = error_word;

@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
       }
     }
     dbg_stamp(p, 2);
-    if (p.fuse_tail) lm_head_tail(p, smem, stream_smem_total(MODE, p.K, NT, B));
+    if (p.fuse_tail) lm_head_tail(p, meta, smem, stream_smem_total(MODE, p.K, NT, B));
   }
 }
 

@@ -175,7 +175,7 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
     tmem_dealloc(tmem_base, TCOLS);
   }
   // decode-sized batches: the last CTA of the grid resolves the rows; the stage ring is free by now
-  if (p.fuse_tail) lm_head_tail(p, smem, (size_t)NI * S * geo.stage_bytes);
+  if (p.fuse_tail) lm_head_tail(p, meta, smem, (size_t)NI * S * geo.stage_bytes);
 }
 
 

@@ -11,6 +11,8 @@
 // buffer) go through fullrow_resolve, an exact radix-select pass over the whole row.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "lm_head.cuh"
 #include "tail.cuh"
 
@@ -737,6 +739,7 @@ int launch_topk_threshold(const void* logits, int dtype, long long ld, int B, in
 // what the kernels receive.
 static __device__ __align__(256) unsigned char g_static_scratch[VQK_STATIC_SCRATCH_BYTES];
 static void* g_static_scratch_ptr[64];  // per device, filled on the first call there
+static std::mutex g_static_scratch_mu;   // ... which may come from several host threads at once
 
 int sample_static(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, long long* tokens,
                   float* scores, cudaStream_t st) {
@@ -744,10 +747,13 @@ int sample_static(const void* logits, int dtype, long long ld, int B, int V, con
   int dev = 0;
   VQK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return VQK_ERR_INVALID;
-  if (!g_static_scratch_ptr[dev]) {  // set-up: once per device, with that device current
-    void* ptr = nullptr;
-    VQK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
-    g_static_scratch_ptr[dev] = ptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (!g_static_scratch_ptr[dev]) {  // set-up: once per device, with that device current
+      void* ptr = nullptr;
+      VQK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+      g_static_scratch_ptr[dev] = ptr;
+    }
   }
   const int nslices = slice_pass_nslices(V);
   // three [B][nslices] arrays, each starting on a 256-byte boundary; all of them are fully

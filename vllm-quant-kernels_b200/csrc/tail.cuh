@@ -77,7 +77,54 @@ __device__ __forceinline__ float h16_key_to_float(uint32_t k) {
   const uint32_t b = (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
   return __half2float(__ushort_as_half((unsigned short)b));
 }
+// the same key from the fp16 bits
+__device__ __forceinline__ uint32_t h16_bits_key(uint32_t b) {
+  b &= 0xffffu;
+  if ((b & 0x7fffu) == 0) b = 0;
+  return (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+}
 constexpr uint32_t kKeyLowestFinite = 0x0400u;  // key(-65504); key(-inf) = 0x03ff sorts below
+
+// k-th largest of the 16-bit keys a warp holds in registers (key[j] of lane l; unused slots hold 0,
+// below every candidate >= kKeyLowestFinite that can win), three key bits per round: each round
+// counts the keys >= seven thresholds at once (the counts packed ten bits apiece into three words,
+// so a round costs three warp reductions instead of one per bit).  At least k keys must be
+// >= kKeyLowestFinite.  Result in every lane.
+template <int R>
+__device__ __forceinline__ uint32_t warp_kth_largest_reg(const uint32_t (&key)[R], int k) {
+  static_assert(R * 32 < 1024, "a count must fit ten bits");
+  uint32_t prefix = 0;
+#pragma unroll 1
+  for (int shift = 13; shift >= -2; shift -= 3) {
+    // thresholds prefix | t << shift, t = 1..7 (the last round, shift = -2, has one bit left: t = 1 only)
+    const int sh = shift < 0 ? 0 : shift;
+    const int nt = shift < 0 ? 1 : 7;
+    uint32_t c0 = 0, c1 = 0, c2 = 0;  // counts of t = 1..3 | 4..6 | 7
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const uint32_t kj = key[j];
+      c0 += (kj >= (prefix | (1u << sh))) + ((uint32_t)(nt > 1 && kj >= (prefix | (2u << sh))) << 10) +
+            ((uint32_t)(nt > 1 && kj >= (prefix | (3u << sh))) << 20);
+      c1 += (uint32_t)(nt > 1 && kj >= (prefix | (4u << sh))) + ((uint32_t)(nt > 1 && kj >= (prefix | (5u << sh))) << 10) +
+            ((uint32_t)(nt > 1 && kj >= (prefix | (6u << sh))) << 20);
+      c2 += (uint32_t)(nt > 1 && kj >= (prefix | (7u << sh)));
+    }
+    c0 = __reduce_add_sync(0xffffffffu, c0);
+    c1 = __reduce_add_sync(0xffffffffu, c1);
+    c2 = __reduce_add_sync(0xffffffffu, c2);
+    // counts fall as t grows: take the largest t whose count still reaches k
+    uint32_t t = 0;
+    if ((int)(c0 & 1023u) >= k) t = 1;
+    if ((int)((c0 >> 10) & 1023u) >= k) t = 2;
+    if ((int)(c0 >> 20) >= k) t = 3;
+    if ((int)(c1 & 1023u) >= k) t = 4;
+    if ((int)((c1 >> 10) & 1023u) >= k) t = 5;
+    if ((int)(c1 >> 20) >= k) t = 6;
+    if ((int)c2 >= k) t = 7;
+    prefix |= t << sh;
+  }
+  return prefix;
+}
 
 // k-th largest of n keys in shared memory (n >= k >= 1) by bisection on the key bits `hi` down to
 // `lo`: the largest x with count(key >= x) >= k.  Whole warp; result in every lane.
@@ -186,6 +233,47 @@ static __device__ __noinline__ void warp_topp_gumbel(const float* cv, const int*
   *t_out = t;
 }
 
+// The same for n <= 64 survivors (the usual case: k + ties), held two per lane in registers: the
+// mass above each survivor is summed over shuffles, the two Gumbel draws of a lane run side by side.
+static __device__ __noinline__ void warp_topp_gumbel64(const float* cv, const int* ct, int n, float T, float top_p, int seed,
+                                                       int lane, float* s_out, int* t_out) {
+  const bool h0 = lane < n, h1 = lane + 32 < n;
+  const float y0 = h0 ? cv[lane] / T : -INFINITY, y1 = h1 ? cv[lane + 32] / T : -INFINITY;
+  const int t0 = h0 ? ct[lane] : 0x7fffffff, t1 = h1 ? ct[lane + 32] : 0x7fffffff;
+  bool a0 = h0, a1 = h1;
+  if (top_p < 1.f) {
+    float mx = fmaxf(y0, y1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const unsigned long long w0 = h0 ? (unsigned long long)((double)expf(y0 - mx) * 1099511627776.0) : 0ull;
+    const unsigned long long w1 = h1 ? (unsigned long long)((double)expf(y1 - mx) * 1099511627776.0) : 0ull;
+    unsigned long long z = w0 + w1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+    const double target = (double)top_p * (double)z;
+    unsigned long long ab0 = 0, ab1 = 0;
+#pragma unroll 4
+    for (int src = 0; src < 32; ++src) {
+      const float ys0 = __shfl_sync(0xffffffffu, y0, src), ys1 = __shfl_sync(0xffffffffu, y1, src);
+      const unsigned long long ws0 = __shfl_sync(0xffffffffu, w0, src), ws1 = __shfl_sync(0xffffffffu, w1, src);
+      if (ys0 > y0) ab0 += ws0;
+      if (ys1 > y0) ab0 += ws1;
+      if (ys0 > y1) ab1 += ws0;
+      if (ys1 > y1) ab1 += ws1;
+    }
+    a0 = a0 && ((double)ab0 < target);
+    a1 = a1 && ((double)ab1 < target);
+  }
+  const float g0 = gumbel_noise(seed, (uint32_t)t0), g1 = gumbel_noise(seed, (uint32_t)t1);
+  float s = a0 ? y0 + g0 : -INFINITY;
+  int t = a0 ? t0 : 0x7fffffff;
+  const float s1 = a1 ? y1 + g1 : -INFINITY;
+  if (a1 && better(s1, t1, s, t)) { s = s1; t = t1; }
+  warp_best_pair(s, t);
+  *s_out = s;
+  *t_out = t;
+}
+
 // Sharded step: exchange this rank's record of row b and merge the shards.  Whole warp; writes the
 // row's token / score.  `scratch` is the warp's scratch (region A is overwritten).
 template <typename CandAt>
@@ -204,7 +292,9 @@ __device__ inline void tail_exchange_row(const PeerTable& pt, const RowMeta& m, 
     } else {
       __syncwarp();
       const int kept = warp_topk_inplace(mv, mt, r.total, m.top_k, lane);
-      if (kept <= kTailSurvCap)
+      if (kept <= 64)
+        warp_topp_gumbel64(mv, mt, kept, m.T, m.top_p, m.seed, lane, &s, &t);
+      else if (kept <= kTailSurvCap)
         warp_topp_gumbel(mv, mt, kept, m.T, m.top_p, m.seed, reinterpret_cast<float*>(scratch + kTailOffY),
                          reinterpret_cast<unsigned long long*>(scratch + kTailOffW), scratch + kTailOffAlive, lane, &s, &t);
     }
@@ -228,15 +318,14 @@ struct TailArgs {
   float* scores;
   uint8_t* records;
   int single_shard;
-  unsigned long long* dbg;
+  unsigned long long* dbg;  // null, or this CTA's 16 time stamps (measurement aid)
 };
 
 // One row, one warp.  Returns 1 when the row is done, 0 when it has to go to the full-row kernel,
 // 2 when it is resolved as far as this shard goes and its record (survivors in cv / ct, count in
-// *nsv_out) still has to be exchanged.  `dry`: rehearsal - same code, nothing is written, no verdict.
-static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, uint8_t* scratch, int lane, bool dry, bool exchange,
-                                             int* nsv_out, float* win_s, int* win_t) {
-  const RowMeta m = decode_row(a.sp, b);
+// *nsv_out, or the winner in *win_s / *win_t) still has to be exchanged.
+static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, const RowMeta& m, int b, uint8_t* scratch, int lane,
+                                                    bool exchange, int* nsv_out, float* win_s, int* win_t) {
   const int nsl = a.nslices;
   const long long voff = a.sp.vocab_offset;
   const unsigned lt = (1u << lane) - 1u;
@@ -256,7 +345,7 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, ui
     *win_s = s;
     *win_t = (int)tok;
     if (exchange) return 2;
-    if (lane == 0 && !dry) {
+    if (lane == 0) {
       tail_write_header(a.records, b, s, (int)tok, 0, 0);
       if (a.tokens) a.tokens[b] = tok;
       if (a.scores) a.scores[b] = s;
@@ -285,21 +374,11 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, ui
     nfin += (qk[j] >= kKeyLowestFinite);
   }
   nfin = __reduce_add_sync(0xffffffffu, nfin);
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[5] = t_; }
   // 2. tau0 = K-th largest CTA maximum: K distinct logits are >= it, so the K-th largest logit is
   //    (bisection on the 16 key bits; every round is kTailQuadRegs compares and one warp vote)
   uint32_t tau0 = kKeyLowestFinite;
-  if (nfin >= K) {
-    uint32_t prefix = 0;
-#pragma unroll 1
-    for (int bit = 15; bit >= 0; --bit) {
-      const uint32_t cand = prefix | (1u << bit);
-      int c = 0;
-#pragma unroll
-      for (int j = 0; j < kTailQuadRegs; ++j) c += (qk[j] >= cand);
-      if (__reduce_add_sync(0xffffffffu, c) >= K) prefix = cand;
-    }
-    tau0 = prefix;
-  }
+  if (nfin >= K) tau0 = warp_kth_largest_reg(qk, K);
   if (tau0 < kKeyLowestFinite) tau0 = kKeyLowestFinite;
   // 3. the CTAs that can hold a logit >= tau0
   int nsel = 0;
@@ -313,6 +392,7 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, ui
   }
   if (nsel > kTailQuadCap) return 0;
   __syncwarp();
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[6] = t_; }
   // 4. trip two: the list records of their slices (two 16-byte loads each, up to kTailRecRegs per lane
   //    in flight at once); every listed value >= tau0 is staged as (key, token); witnesses are folded
   //    to a maximum
@@ -336,11 +416,9 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, ui
     int mine_n = 0;
 #pragma unroll
     for (int r = 0; r < kTailRecRegs; ++r) {
-      const uint32_t k0 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].x & 0xffffu))));
-      const uint32_t k1 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].x >> 16))));
-      const uint32_t k2 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].y & 0xffffu))));
-      const uint32_t k3 = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].y >> 16))));
-      const uint32_t kw = h16_key(__half2float(__ushort_as_half((unsigned short)(rv[r].z & 0xffffu))));
+      const uint32_t k0 = h16_bits_key(rv[r].x), k1 = h16_bits_key(rv[r].x >> 16);
+      const uint32_t k2 = h16_bits_key(rv[r].y), k3 = h16_bits_key(rv[r].y >> 16);
+      const uint32_t kw = h16_bits_key(rv[r].z);
       if (k0 >= tau0) wkey = max(wkey, kw);  // a slice whose maximum is below tau0 hides nothing that matters
       mine_n += (k0 >= tau0) + (k1 >= tau0) + (k2 >= tau0) + (k3 >= tau0);
       rv[r] = make_uint4(k0, k1, k2, k3);    // keep the keys
@@ -365,11 +443,23 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, ui
   }
   wkey = __reduce_max_sync(0xffffffffu, wkey);
   __syncwarp();
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[7] = t_; }
   // 5. t_k: the K-th largest staged value (every staged value survives when fewer than K exist)
   uint32_t tk = kKeyLowestFinite;
-  if (ne >= K) tk = warp_kth_largest_key([&](int i) { return st[i].x; }, ne, K, 15, 0, lane);
+  if (ne >= K) {
+    if (ne <= 128) {  // the usual case: a handful of keys per lane, kept in registers
+      uint32_t sk[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sk[j] = j * 32 + lane < ne ? st[j * 32 + lane].x : 0u;
+      const uint32_t prefix = warp_kth_largest_reg(sk, K);
+      tk = prefix;
+    } else {
+      tk = warp_kth_largest_key([&](int i) { return st[i].x; }, ne, K, 15, 0, lane);
+    }
+  }
   // 6. the proof: no slice we looked at hides a value >= t_k (the others have maximum < tau0 <= t_k)
-  if (wkey >= tk && !dry) return 0;
+  if (wkey >= tk) return 0;
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[10] = t_; }
   // 7. survivors (>= t_k, ties kept), with their GLOBAL token ids
   int nsv = 0;
 #pragma unroll 1
@@ -385,26 +475,27 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, ui
     }
     nsv += __popc(mask);
   }
-  if (nsv > kTailSurvCap) {
-    if (!dry) return 0;
-    nsv = kTailSurvCap;
-  }
+  if (nsv > kTailSurvCap) return 0;
   __syncwarp();
   *nsv_out = nsv;
   if (exchange) return nsv > VQK_RECORD_CAP ? 0 : 2;  // (the full-row kernel reports an overflowing record)
-  if (a.records && !dry) {  // shard record: the local top-k survivors; top-p needs the union of the shards
+  if (a.records) {  // shard record: the local top-k survivors; top-p needs the union of the shards
     Cand* out = reinterpret_cast<Cand*>(a.records + (size_t)b * VQK_RECORD_BYTES + sizeof(RecordHeader));
     for (int i = lane; i < nsv && i < VQK_RECORD_CAP; i += 32) out[i] = Cand{cv[i], ct[i]};
     if (lane == 0)
       tail_write_header(a.records, b, -INFINITY, -1, min(nsv, VQK_RECORD_CAP), nsv > VQK_RECORD_CAP ? VQK_RECORD_FLAG_OVERFLOW : 0);
   }
   if (!a.single_shard) return 1;
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[11] = t_; }
   // 8. top-p over the survivors, then the Gumbel argmax
   float s;
   int t;
-  warp_topp_gumbel(cv, ct, nsv, m.T, m.top_p, m.seed, reinterpret_cast<float*>(scratch + kTailOffY),
-                   reinterpret_cast<unsigned long long*>(scratch + kTailOffW), scratch + kTailOffAlive, lane, &s, &t);
-  if (lane == 0 && !dry) {
+  if (nsv <= 64)
+    warp_topp_gumbel64(cv, ct, nsv, m.T, m.top_p, m.seed, lane, &s, &t);
+  else
+    warp_topp_gumbel(cv, ct, nsv, m.T, m.top_p, m.seed, reinterpret_cast<float*>(scratch + kTailOffY),
+                     reinterpret_cast<unsigned long long*>(scratch + kTailOffW), scratch + kTailOffAlive, lane, &s, &t);
+  if (lane == 0) {
     if (a.tokens) a.tokens[b] = t;
     if (a.scores) a.scores[b] = s;
   }
@@ -413,15 +504,21 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, int b, ui
 
 // Called by every thread of every CTA once its slice results are written.  `scratch` is shared
 // memory of the CTA that is no longer in use, `scratch_bytes` of it (at least kTailWarpBytes).
-__device__ inline void lm_head_tail(const LmHeadParams& p, uint8_t* scratch, size_t scratch_bytes) {
+// `meta`: the rows' sampling parameters as the kernel decoded them at its start (shared memory).
+__device__ inline void lm_head_tail(const LmHeadParams& p, const RowMeta* meta, uint8_t* scratch, size_t scratch_bytes) {
   __shared__ int s_last;
-  __threadfence();  // this thread's slice results are visible device-wide before the ticket is taken
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+  __shared__ RowMeta s_meta[kTailMaxBatch];  // a copy outside the scratch, which may overlay `meta`
+  __syncthreads();  // every thread's slice results are written ...
+  if (threadIdx.x == 0) {
+    __threadfence();  // ... and visible device-wide before the ticket is taken (the fence is cumulative over the barrier)
+    s_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+    if (s_last) __threadfence();
+  }
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
   dbg_stamp(p, 3);
+  if (threadIdx.x < p.B && threadIdx.x < kTailMaxBatch) s_meta[threadIdx.x] = meta[threadIdx.x];
+  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int nw = min((int)(blockDim.x >> 5), kTailMaxWarps);
   nw = min(nw, (int)(scratch_bytes / kTailWarpBytes));
@@ -430,15 +527,16 @@ __device__ inline void lm_head_tail(const LmHeadParams& p, uint8_t* scratch, siz
     TailArgs a;
     a.sp = p.sp; a.slice_max = p.slice_max; a.part_score = p.part_score; a.part_token = p.part_token;
     a.lists = p.lists; a.nslices = p.nslices; a.tokens = p.tokens; a.scores = p.scores;
-    a.records = p.records; a.single_shard = p.single_shard; a.dbg = p.dbg;
+    a.records = p.records; a.single_shard = p.single_shard;
+    a.dbg = p.dbg ? p.dbg + (size_t)blockIdx.x * 16 : nullptr;
     const bool exchange = p.peer.G > 0;
     for (int b = warp; b < p.B; b += nw) {
       int nsv = 0, wt = 0;
       float ws = 0.f;
       int r = 0;
-      if (p.fuse_tail == 1) r = tail_resolve_row(a, b, mine, lane, false, exchange, &nsv, &ws, &wt);  // 2: A/B runs, every row to the full-row kernel
+      const RowMeta m = s_meta[b];
+      if (p.fuse_tail == 1) r = tail_resolve_row(a, m, b, mine, lane, exchange, &nsv, &ws, &wt);  // 2: A/B runs, every row to the full-row kernel
       if (r == 2) {
-        const RowMeta m = decode_row(p.sp, b);
         const float* cv = reinterpret_cast<const float*>(mine + kTailOffCv);
         const int* ct = reinterpret_cast<const int*>(mine + kTailOffCt);
         if (m.flags & ROW_CAND)

@@ -94,24 +94,14 @@ __host__ __device__ inline uint32_t instr_desc(bool int8, int bn) {
   return d;
 }
 
-// Which vocab rows a CTA works on, as a sequence of tiles.
-//   interleaved  tile n = rows [(blockIdx.x + n * gridDim.x) * BM, + BM): every CTA takes whole
-//                128-row tiles round-robin;
-//   contiguous   the CTA owns rows [row_begin, row_end), cut into full tiles followed by tail
-//                tiles of `tail_rows` rows (fetched through a second tensor map with that box
-//                height), so that all CTAs stream the same number of bytes although the tile
-//                count does not divide by the grid.  A tail tile still costs a full tile's MMAs
-//                (rows beyond it are stale shared memory whose results nobody reads).
+// Which vocab rows a CTA works on: its n-th tile is rows [(blockIdx.x + n * gridDim.x) * BM, + BM),
+// whole 128-row tiles round-robin over the grid; the last tile of the matrix may be short.
 struct TileSched {
-  int row_begin, row_end, nfull, ntail, tail_rows, stride_rows;
-  __device__ __forceinline__ int count() const { return nfull + ntail; }
-  __device__ __forceinline__ bool is_tail(int n) const { return n >= nfull; }
-  __device__ __forceinline__ int row0(int n) const {
-    if (stride_rows) return row_begin + n * stride_rows;
-    return n < nfull ? row_begin + n * BM : row_begin + nfull * BM + (n - nfull) * tail_rows;
-  }
+  int row_begin, row_end, ntiles, stride_rows;
+  __device__ __forceinline__ int count() const { return ntiles; }
+  __device__ __forceinline__ int row0(int n) const { return row_begin + n * stride_rows; }
   __device__ __forceinline__ int limit(int n) const {  // one past the last row of tile n that exists
-    const int r = row0(n) + (n < nfull ? BM : tail_rows);
+    const int r = row0(n) + BM;
     return r < row_end ? r : row_end;
   }
 };
@@ -120,28 +110,8 @@ __device__ __forceinline__ TileSched sched_interleaved(int V) {
   const int ntiles = (V + BM - 1) / BM;
   t.row_begin = (int)blockIdx.x * BM;
   t.row_end = V;
-  t.nfull = (int)blockIdx.x < ntiles ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  t.ntail = 0;
-  t.tail_rows = 0;
+  t.ntiles = (int)blockIdx.x < ntiles ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   t.stride_rows = (int)gridDim.x * BM;
-  return t;
-}
-// `per` rows per CTA (a multiple of 16); tail_rows = per % BM (0: the only partial tile is the one at V)
-__device__ __forceinline__ TileSched sched_contiguous(int V, int per) {
-  TileSched t;
-  const long long b = (long long)blockIdx.x * per;
-  t.row_begin = (int)(b < V ? b : V);
-  t.row_end = (int)(b + per < V ? b + per : V);
-  const int len = t.row_end - t.row_begin;
-  t.tail_rows = per % BM;
-  t.stride_rows = 0;
-  if (t.tail_rows) {
-    t.nfull = len / BM;
-    t.ntail = (len - t.nfull * BM + t.tail_rows - 1) / t.tail_rows;
-  } else {
-    t.nfull = (len + BM - 1) / BM;
-    t.ntail = 0;
-  }
   return t;
 }
 
@@ -160,10 +130,7 @@ __device__ __forceinline__ float key_to_float(int k) {
 // NI: independent MMA pipelines ("lanes") in the CTA.  The CTA's n-th tile is computed by lane
 // n % NI into that lane's accumulator (n / NI) % 2, at TMEM columns ((n % NI) * 2 + buffer) * BN,
 // and announced / released through tfull / tempty at the same index.
-// KSPLIT: the NI pipelines work on the SAME tile, each on its share of K, into its own accumulator
-// (buffer l * 2 + (n & 1) for the CTA's n-th tile); the epilogue waits for all of them and adds the
-// partial sums in pipeline order.
-template <int EPI, int BN, int NI = 1, bool KSPLIT = false>
+template <int EPI, int BN, int NI = 1>
 __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, int lane, uint32_t tmem_base,
                                               uint64_t* tfull, uint64_t* tempty, volatile int* abort_flag,
                                               const RowMeta* meta, int* sstate, const TileSched& sched, Cand* qlists,
@@ -195,8 +162,8 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
 
     const int mytiles = sched.count();
     for (int tcount = 0; tcount < mytiles; ++tcount) {
-      const int buf = KSPLIT ? (tcount & 1) : (tcount % NI) * 2 + ((tcount / NI) & 1);
-      const uint32_t tph = KSPLIT ? (uint32_t)(tcount >> 1) & 1u : (uint32_t)((tcount / NI) >> 1) & 1u;
+      const int buf = (tcount % NI) * 2 + ((tcount / NI) & 1);
+      const uint32_t tph = (uint32_t)((tcount / NI) >> 1) & 1u;
       const int tile_row0 = sched.row0(tcount), tile_lim = sched.limit(tcount);
       const int row = tile_row0 + q * 32 + lane;
       const bool rok = row < tile_lim;
@@ -206,29 +173,12 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
       if constexpr (EPI == 0) rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[rowc]);
       const float bias = p.bias ? __half2float(p.bias[rowc]) : 0.f;
       if (!mbar_wait_warp(&tfull[buf], tph, abort_flag)) break;
-      if constexpr (KSPLIT) {
-        bool all = true;
-#pragma unroll
-        for (int l = 1; l < NI; ++l) all = all && mbar_wait_warp(&tfull[l * 2 + buf], tph, abort_flag);
-        if (!all) break;
-      }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
       for (int ch = 0; ch < nchunk; ++ch) {
         const int c0 = ch * 16;
         uint32_t r[16];
         tmem_ld16(taddr + (uint32_t)c0, r);
-        if constexpr (KSPLIT) {
-          static_assert(!KSPLIT || EPI != 1, "partial sums are added as fp32");
-#pragma unroll
-          for (int l = 1; l < NI; ++l) {
-            uint32_t r2[16];
-            tmem_ld16(taddr + (uint32_t)(l * 2 * BN + c0), r2);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-          }
-        }
         // which of the 16 columns take the candidate path / exist at all
         int myflags = 0;
         if (lane < 16 && c0 + lane < B && p.do_sample) myflags = meta[c0 + lane].flags | 0x100;
@@ -354,13 +304,7 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&tempty[buf]);
-        if constexpr (KSPLIT) {
-#pragma unroll
-          for (int l = 1; l < NI; ++l) mbar_arrive(&tempty[l * 2 + buf]);
-        }
-      }
+      if (lane == 0) mbar_arrive(&tempty[buf]);
     }
     __syncwarp();
     if (p.do_sample) {
