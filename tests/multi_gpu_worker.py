@@ -42,7 +42,7 @@ def main():
                                t(kw.get("top_p"), torch.float32), None, 0, V)
 
     comm = VqkComm(rank, world)
-    peer = VqkPeer(rank, world, max_rows=16)
+    peer = VqkPeer(rank, world, max_rows=32)
     a, b = shard_bounds(V, world, rank)
     for mode in ("int8", "mxfp4"):
         q, s = LH.quantize_weight(mode, w)

@@ -174,7 +174,8 @@ extern "C" const char* vqk_strerror(int s) {
     case VQK_ERR_ARCH: return "device is not sm_100 (B200); there is no fallback path";
     case VQK_ERR_COMM: return "NCCL unavailable or collective failed";
     case VQK_ERR_TOO_LARGE:
-      return "size exceeds a fixed maximum (vqk_sample_static: at most 64 rows of at most 262144 columns)";
+      return "size exceeds a fixed maximum (vqk_sample_static: at most 64 rows of at most 262144 columns; "
+             "vqk_peer: the max_rows it was created with)";
   }
   return "unknown status";
 }
@@ -182,14 +183,14 @@ extern "C" const char* vqk_strerror(int s) {
 extern "C" int vqk_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int vqk_device_error(void) {
-  const int b = umma_error_flag(), c = umma_mx_error_flag(), d = peer_error_flag();
-  return (b < 0 || c < 0 || d < 0) ? -1 : (b | c | d);
+  const int a = stream_error_flag(), b = umma_error_flag(), c = umma_mx_error_flag(), d = peer_error_flag();
+  return (a < 0 || b < 0 || c < 0 || d < 0) ? -1 : (a | b | c | d);
 }
 
 extern "C" int vqk_device_error_clear(void) {
   const int zero = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return VQK_ERR_CUDA;
-  if (umma_error_clear() || umma_mx_error_clear()) return VQK_ERR_CUDA;
+  if (stream_error_clear() || umma_error_clear() || umma_mx_error_clear()) return VQK_ERR_CUDA;
   VQK_CUDA(cudaMemcpyToSymbol(g_peer_error, &zero, sizeof(int)));
   return VQK_OK;
 }
@@ -310,16 +311,15 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   if (sp) sd = to_dev(sp);
   // Decode-sized batches: the lm_head kernel's last CTA resolves the rows itself (tail.cuh); the
   // full-row kernel behind it only picks up rows the tail flagged.
-  // The streaming kernel always, the tensor-core kernels when the step is sharded over peer memory
-  // (one kernel instead of three) - on one GPU their tail ran slower than the full-row kernel it
-  // replaces.  VQK_TAIL_MODE (A/B runs): 0 = never, 2 = the tail hands every row to the full-row
-  // kernel, 3 = every kernel.
+  // The streaming kernel only: inside the tensor-core kernels the same tail ran slower than the
+  // full-row kernel it replaces, and the per-column lists cost their epilogues registers.
+  // VQK_TAIL_MODE (A/B runs): 0 = never, 2 = the tail hands every row to the full-row kernel.
   static const int tail_mode = [] {
     const char* e = getenv("VQK_TAIL_MODE");
     const int v = e ? atoi(e) : 1;
-    return v >= 0 && v <= 3 ? v : 1;
+    return v >= 0 && v <= 2 ? v : 1;
   }();
-  const bool tail_here = tail_mode == 3 || !use_umma || peer != nullptr;
+  const bool tail_here = !use_umma;
   const bool fuse_tail = tail_mode && tail_here && sp && B <= kTailMaxBatch && B <= maxcols && nslices <= 1024;
   unsigned int* tickets = nullptr;
   int* error_word = nullptr;

@@ -90,6 +90,8 @@ constexpr int kTailMaxBatch = 16;    // largest batch whose rows the lm_head ker
 size_t stream_smem_bytes(int mode, int K, int NT);
 int stream_max_cols(int mode, int K);  // batch columns one launch can take (0: K too large)
 int launch_lm_head_stream(int mode, const LmHeadParams& p, int grid, cudaStream_t st);
+int stream_error_flag();
+int stream_error_clear();
 
 
 // lm_head_umma.cu: tcgen05 tensor-core kernel for larger batches (FP8, W8A8; K % 128 == 0)

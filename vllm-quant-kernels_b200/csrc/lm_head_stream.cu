@@ -1,16 +1,23 @@
 // Weight-streaming lm_head kernel for small batches (decode): one persistent CTA per SM,
-// 16 warps = 4 groups x 4 warps.  A group owns one 16-row vocab tile at a time and its four
-// warps split K; every lane streams 16 B (8 B / 4 B for the MX modes) of two weight rows
-// straight from HBM into registers in the layout of a warp-level MMA A fragment, so the
-// only per-byte ALU work is the int8 -> fp16 (or E2M1 -> e4m3) expansion.  Activations sit in
-// shared memory, pre-arranged as B fragments.  The epilogue applies the mode's scale,
-// rounds to fp16 exactly like the reference launchers, optionally stores the logits, and
-// feeds the sampler (per-slice maxima, per-slice Gumbel winners) without a second pass.
+// 16 streaming warps = 4 groups x 4 warps, plus one epilogue warp per group.  A group owns one 16-row
+// vocab tile at a time and its four warps split K; every lane streams 16 B (8 B / 4 B for the MX
+// modes) of two weight rows straight from HBM into registers in the layout of a warp-level MMA A
+// fragment, so the only per-byte ALU work is the int8 -> fp16 (or E2M1 -> e4m3) expansion.
+// Activations sit in shared memory, pre-arranged as B fragments.
+// The streaming warps never wait for one another: at the end of a tile each parks its split-K
+// partial sums in shared memory (two buffers per group, handed over through mbarriers) and goes
+// on with the next tile.  The group's epilogue warp adds the partials, applies the mode's scale,
+// rounds to fp16 exactly like the reference launchers, optionally stores the logits, and feeds
+// the sampler (per-slice lists of the largest logits, per-slice Gumbel winners) without a second
+// pass.  With the epilogue inside the streaming warps (two block barriers per tile) the W8A16
+// kernel ran 9 % slower.  Twenty warps leave 96 registers per thread, which is why a warp keeps ONE
+// set of weight registers and refills it unit by unit instead of double-buffering whole batches.
 //
 // Replaces int8_gmv / int8_gemm / fp8_gemm / int8_w8a8_gemm / mxfp8_gemm / mxfp4_gemm of the
 // reference (src/vllm_quant_kernels/_kernels.py) for batch <= 32.
 #include <stdlib.h>
 
+#include "async_helpers.cuh"
 #include "lm_head.cuh"
 #include "mma_helpers.cuh"
 #include "tail.cuh"
@@ -45,8 +52,9 @@ struct StreamBuf<MODE, U, true> {
   uint32_t scA[U / 4], scB[U / 4];
 };
 
-constexpr int kThreads = 512;
 constexpr int kGroups = 4;
+constexpr int kStreamWarps = 4 * kGroups;
+constexpr int kThreads = (kStreamWarps + kGroups) * 32;  // warp 16 + g is group g's epilogue warp
 
 // shared memory carve-up (bytes) -----------------------------------------------------------
 __host__ __device__ inline size_t stream_xfrag_bytes(int mode, int K, int NT) {
@@ -56,13 +64,17 @@ __host__ __device__ inline size_t stream_xfrag_bytes(int mode, int K, int NT) {
 __host__ __device__ inline size_t stream_sx_bytes(int mode, int K, int NT) {
   return (mode == VQK_MODE_MXFP8 || mode == VQK_MODE_MXFP4) ? (size_t)(K / GROUP) * NT * 8 * sizeof(float) : 0;
 }
-__host__ __device__ inline size_t stream_red_bytes(int NT) { return (size_t)16 * NT * 128 * 4; }
+// split-K partial sums: [2 buffers][16 warps][NT][128] accumulators
+__host__ __device__ inline size_t stream_red_bytes(int NT) { return (size_t)2 * kStreamWarps * NT * 128 * 4; }
+// per warp group, batch column and tile row: running Gumbel (or greedy) winner of rows without top-k / top-p
+__host__ __device__ inline size_t stream_win_bytes(int NT) { return (size_t)kGroups * NT * 8 * 16 * sizeof(Cand); }
+constexpr size_t kStreamBarBytes = (size_t)(4 * kGroups + 1) * 8;  // full / free barriers of the partial-sum buffers, abort flag
 // per warp group and batch column: the kListLen largest logits of the group's slice (sampler, top-k rows)
 __host__ __device__ inline size_t stream_tlist_bytes(int NT) { return (size_t)kGroups * NT * 8 * kListLen * sizeof(Cand); }
 // (the sampler tail reuses the buffer once the main loop is over: one warp's scratch per batch row)
 __host__ __device__ inline size_t stream_smem_total(int mode, int K, int NT, int B) {
   const size_t main_loop = stream_xfrag_bytes(mode, K, NT) + stream_sx_bytes(mode, K, NT) + stream_red_bytes(NT) +
-                           (size_t)NT * 8 * sizeof(RowMeta) + stream_tlist_bytes(NT);
+                           (size_t)NT * 8 * sizeof(RowMeta) + stream_tlist_bytes(NT) + stream_win_bytes(NT) + kStreamBarBytes;
   const size_t tail = tail_smem_bytes(B < NT * 8 ? B : NT * 8);
   return main_loop > tail ? main_loop : tail;
 }
@@ -77,35 +89,39 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   float* sxf = reinterpret_cast<float*>(smem + stream_xfrag_bytes(MODE, p.K, NT));
   acc_t* red = reinterpret_cast<acc_t*>(smem + stream_xfrag_bytes(MODE, p.K, NT) + stream_sx_bytes(MODE, p.K, NT));
   RowMeta* meta = reinterpret_cast<RowMeta*>(reinterpret_cast<uint8_t*>(red) + stream_red_bytes(NT));
-  Cand* slist = reinterpret_cast<Cand*>(meta + NT * 8) + (size_t)(threadIdx.x >> 7) * NT * 8 * kListLen;  // this group's lists [column][entry]
+  Cand* slist_all = reinterpret_cast<Cand*>(meta + NT * 8);                       // [group][column][entry]
+  Cand* swin = slist_all + (size_t)kGroups * NT * 8 * kListLen;                    // [group][column][tile row]
+  uint64_t* fullb = reinterpret_cast<uint64_t*>(swin + (size_t)kGroups * NT * 8 * 16);  // [group][buffer]: partial sums parked
+  uint64_t* freeb = fullb + 2 * kGroups;                                           // [group][buffer]: partial sums read
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(freeb + 2 * kGroups);
 
   dbg_stamp(p, 0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int group = warp >> 2, wq = warp & 3;
+  const bool is_epi = warp >= kStreamWarps;
+  const int group = (warp >> 2) & (kGroups - 1), wq = warp & 3;
   const int g = lane >> 2, t = lane & 3;
   const int K = p.K, V = p.V, B = p.B;
   const int ngroups = K / GROUP;
   const int nks = (K + 63) / 64;
 
-  // ---- per-thread sampler state: epilogue thread e of a group owns (row e%16, col e/16) ----
-  const int e = tid & 127;
-  const int er = e & 15, ec = e >> 4;
-  // rows without top-k / top-p: the running Gumbel (or greedy) winner of this thread's rows
-  float bs[NT];
-  int bt[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) { bs[nt] = -INFINITY; bt[nt] = 0x7fffffff; }
-  if (p.do_sample)
-    for (int i = threadIdx.x & 127; i < NT * 8 * kListLen; i += 128) slist[i] = Cand{-INFINITY, 0x7fffffff};
+  if (p.do_sample) {
+    for (int i = tid; i < kGroups * NT * 8 * kListLen; i += kThreads) slist_all[i] = Cand{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < kGroups * NT * 8 * 16; i += kThreads) swin[i] = Cand{-INFINITY, 0x7fffffff};
+  }
+  if (tid == 0) {
+    for (int i = 0; i < 2 * kGroups; ++i) {
+      mbar_init(&fullb[i], 128);  // every thread of the group's four warps
+      mbar_init(&freeb[i], 32);   // every lane of the group's epilogue warp
+    }
+    *abort_flag = 0;
+  }
 
   const int ntiles = (V + 15) / 16;
   const size_t rowbytes = (MODE == VQK_MODE_MXFP4) ? (size_t)K / 2 : (size_t)K;
-  acc_t* myred = red + (size_t)warp * NT * 128;
-  const acc_t* gred = red + (size_t)(group * 4) * NT * 128;
+  constexpr int kRedBuf = kStreamWarps * NT * 128;  // accumulators per buffer
+  acc_t* myred = red + (size_t)(warp & (kStreamWarps - 1)) * NT * 128;
 
-  // ---- main loop: a flat sequence of (tile, batch) steps per warp, double-buffered in
-  // registers: the loads of step n+1 are issued before the MMAs of step n, also across tile
-  // boundaries, so the HBM stream of a warp never waits for its own arithmetic.
+  // ---- main loop: a flat sequence of (tile, batch) steps per warp; a batch is U units.
   // EVEN (V % 16 == 0, every warp owns `per` whole units, per % U == 0) removes every bounds
   // test and zero fill from the inner loop; the instruction count per byte is what decides
   // whether this kernel reaches the HBM rate.
@@ -117,60 +133,69 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   const int ubeg = wq * per, uend = EVEN ? ubeg + per : min(units, ubeg + per);
   const int nb = (per + U - 1) / U;        // batches per tile (same for the 4 warps of a group)
   const bool sc_aligned = MX && (EVEN || (((ngroups & 3) == 0) && ((per & 3) == 0)));
-  StreamBuf<MODE, U> buf0, buf1;
+  StreamBuf<MODE, U> buf;
 
-  auto issue = [&](StreamBuf<MODE, U>& f, int tile, int bi) {
+  // where batch `bi` of tile `tile` lies for this lane
+  struct BatchAddr {
+    const uint8_t *pA, *pB, *sA, *sB;
+    int u0;
+  };
+  auto locate = [&](int tile, int bi) {
     const int row0 = tile * 16;
     const int rA = EVEN ? row0 + g : min(row0 + g, V - 1);
     const int rB = EVEN ? row0 + g + 8 : min(row0 + g + 8, V - 1);
-    const int u0 = ubeg + bi * U;
-    const uint8_t* pA = p.w + (size_t)rA * rowbytes + (size_t)u0 * UB + t * LB;
-    const uint8_t* pB = p.w + (size_t)rB * rowbytes + (size_t)u0 * UB + t * LB;
+    BatchAddr a;
+    a.u0 = ubeg + bi * U;
+    a.pA = p.w + (size_t)rA * rowbytes + (size_t)a.u0 * UB + t * LB;
+    a.pB = p.w + (size_t)rB * rowbytes + (size_t)a.u0 * UB + t * LB;
+    a.sA = a.sB = nullptr;
+    if constexpr (MX) {
+      const uint8_t* ws = reinterpret_cast<const uint8_t*>(p.wscale);
+      a.sA = ws + (size_t)rA * ngroups + a.u0;
+      a.sB = ws + (size_t)rB * ngroups + a.u0;
+    }
+    return a;
+  };
+  // unit u of a batch into its registers
+  auto load_unit = [&](StreamBuf<MODE, U>& f, const BatchAddr& a, int u) {
     if constexpr (!MX) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (EVEN || (u0 + u < uend && (u0 + u) * 64 + t * 16 + 16 <= K)) {
-          f.a[u] = ldg_stream16(pA + u * UB);
-          f.b[u] = ldg_stream16(pB + u * UB);
-        } else {
-          f.a[u] = make_uint4(0, 0, 0, 0);
-          f.b[u] = make_uint4(0, 0, 0, 0);
-        }
+      if (EVEN || (a.u0 + u < uend && (a.u0 + u) * 64 + t * 16 + 16 <= K)) {
+        f.a[u] = ldg_stream16(a.pA + u * UB);
+        f.b[u] = ldg_stream16(a.pB + u * UB);
+      } else {
+        f.a[u] = make_uint4(0, 0, 0, 0);
+        f.b[u] = make_uint4(0, 0, 0, 0);
       }
     } else {
       constexpr int QW = StreamBuf<MODE, U>::QW;
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (EVEN || u0 + u < uend) {
-          if constexpr (MODE == VQK_MODE_MXFP8) {
-            uint2 va = ldg_stream8(pA + u * UB), vb = ldg_stream8(pB + u * UB);
-            f.qa[u][0] = va.x; f.qa[u][QW - 1] = va.y; f.qb[u][0] = vb.x; f.qb[u][QW - 1] = vb.y;
-          } else {
-            f.qa[u][0] = ldg_stream4(pA + u * UB);
-            f.qb[u][0] = ldg_stream4(pB + u * UB);
-          }
+      if (EVEN || a.u0 + u < uend) {
+        if constexpr (MODE == VQK_MODE_MXFP8) {
+          uint2 va = ldg_stream8(a.pA + u * UB), vb = ldg_stream8(a.pB + u * UB);
+          f.qa[u][0] = va.x; f.qa[u][QW - 1] = va.y; f.qb[u][0] = vb.x; f.qb[u][QW - 1] = vb.y;
         } else {
-#pragma unroll
-          for (int q = 0; q < QW; ++q) { f.qa[u][q] = 0; f.qb[u][q] = 0; }
+          f.qa[u][0] = ldg_stream4(a.pA + u * UB);
+          f.qb[u][0] = ldg_stream4(a.pB + u * UB);
         }
+      } else {
+#pragma unroll
+        for (int q = 0; q < QW; ++q) { f.qa[u][q] = 0; f.qb[u][q] = 0; }
       }
-      const uint8_t* ws = reinterpret_cast<const uint8_t*>(p.wscale);
-      const uint8_t* sA = ws + (size_t)rA * ngroups + u0;
-      const uint8_t* sB = ws + (size_t)rB * ngroups + u0;
+    }
+  };
+  // MX: the E8M0 bytes of units 4q .. 4q + 3
+  auto load_scales = [&](StreamBuf<MODE, U>& f, const BatchAddr& a, int q) {
+    if constexpr (MX) {
+      if (EVEN || (sc_aligned && a.u0 + 4 * q + 4 <= uend)) {
+        f.scA[q] = __ldg(reinterpret_cast<const unsigned int*>(a.sA + 4 * q));
+        f.scB[q] = __ldg(reinterpret_cast<const unsigned int*>(a.sB + 4 * q));
+      } else {
+        f.scA[q] = 0; f.scB[q] = 0;
 #pragma unroll
-      for (int q = 0; q < U / 4; ++q) {
-        if (EVEN || (sc_aligned && u0 + 4 * q + 4 <= uend)) {
-          f.scA[q] = __ldg(reinterpret_cast<const unsigned int*>(sA + 4 * q));
-          f.scB[q] = __ldg(reinterpret_cast<const unsigned int*>(sB + 4 * q));
-        } else {
-          f.scA[q] = 0; f.scB[q] = 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (u0 + 4 * q + j < uend) {
-              f.scA[q] |= (uint32_t)__ldg(sA + 4 * q + j) << (8 * j);
-              f.scB[q] |= (uint32_t)__ldg(sB + 4 * q + j) << (8 * j);
-            }
-        }
+        for (int j = 0; j < 4; ++j)
+          if (a.u0 + 4 * q + j < uend) {
+            f.scA[q] |= (uint32_t)__ldg(a.sA + 4 * q + j) << (8 * j);
+            f.scB[q] |= (uint32_t)__ldg(a.sB + 4 * q + j) << (8 * j);
+          }
       }
     }
   };
@@ -181,77 +206,74 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0;
 
-  auto consume = [&](const StreamBuf<MODE, U>& f, int bi) {
-    const int u0 = ubeg + bi * U;
+  // the MMAs of unit u of the batch that starts at unit u0
+  auto consume_unit = [&](const StreamBuf<MODE, U>& f, int u0, int u) {
+    if (!(EVEN || u0 + u < uend)) return;
     const uint2* xf = xfrag + (size_t)u0 * (MM * NT * 32) + lane;   // fragment (unit, i, nt) at ((u*MM+i)*NT+nt)*32
     if constexpr (!MX) {
+      const uint32_t wa[4] = {f.a[u].x, f.a[u].y, f.a[u].z, f.a[u].w};
+      const uint32_t wb[4] = {f.b[u].x, f.b[u].y, f.b[u].z, f.b[u].w};
+      if constexpr (MODE == VQK_MODE_W8A16) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (EVEN || u0 + u < uend) {
-          const uint32_t wa[4] = {f.a[u].x, f.a[u].y, f.a[u].z, f.a[u].w};
-          const uint32_t wb[4] = {f.b[u].x, f.b[u].y, f.b[u].z, f.b[u].w};
-          if constexpr (MODE == VQK_MODE_W8A16) {
+        for (int i = 0; i < 4; ++i) {
+          uint32_t a0, a1, a2, a3;
+          int8x4_to_half2_even_odd(wa[i], a0, a2);
+          int8x4_to_half2_even_odd(wb[i], a1, a3);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t a0, a1, a2, a3;
-              int8x4_to_half2_even_odd(wa[i], a0, a2);
-              int8x4_to_half2_even_odd(wb[i], a1, a3);
+          for (int nt = 0; nt < NT; ++nt) {
+            uint2 bf = xf[((u * MM + i) * NT + nt) * 32];
+            mma_f16(acc[nt], a0, a1, a2, a3, bf.x, bf.y);
+          }
+        }
+      } else {
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                uint2 bf = xf[((u * MM + i) * NT + nt) * 32];
-                mma_f16(acc[nt], a0, a1, a2, a3, bf.x, bf.y);
-              }
-            }
-          } else {
+        for (int i = 0; i < 2; ++i) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                uint2 bf = xf[((u * MM + i) * NT + nt) * 32];
-                if constexpr (MODE == VQK_MODE_W8A8)
-                  mma_s8(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
-                else
-                  mma_e4m3(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
-              }
-            }
+          for (int nt = 0; nt < NT; ++nt) {
+            uint2 bf = xf[((u * MM + i) * NT + nt) * 32];
+            if constexpr (MODE == VQK_MODE_W8A8)
+              mma_s8(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
+            else
+              mma_e4m3(acc[nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], bf.x, bf.y);
           }
         }
       }
     } else {
       constexpr int QW = StreamBuf<MODE, U>::QW;
       const float* sxp = sxf + (size_t)u0 * (NT * 8) + 2 * t;
+      uint32_t a0, a1, a2, a3;
+      if constexpr (MODE == VQK_MODE_MXFP8) {
+        a0 = f.qa[u][0]; a2 = f.qa[u][QW - 1]; a1 = f.qb[u][0]; a3 = f.qb[u][QW - 1];
+      } else {
+        e2m1x8_to_e4m3_even_odd(f.qa[u][0], a0, a2);
+        e2m1x8_to_e4m3_even_odd(f.qb[u][0], a1, a3);
+      }
+      const float fa = e8m0_to_f32((f.scA[u >> 2] >> (8 * (u & 3))) & 0xff);
+      const float fb = e8m0_to_f32((f.scB[u >> 2] >> (8 * (u & 3))) & 0xff);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (EVEN || u0 + u < uend) {
-          uint32_t a0, a1, a2, a3;
-          if constexpr (MODE == VQK_MODE_MXFP8) {
-            a0 = f.qa[u][0]; a2 = f.qa[u][QW - 1]; a1 = f.qb[u][0]; a3 = f.qb[u][QW - 1];
-          } else {
-            e2m1x8_to_e4m3_even_odd(f.qa[u][0], a0, a2);
-            e2m1x8_to_e4m3_even_odd(f.qb[u][0], a1, a3);
-          }
-          const float fa = e8m0_to_f32((f.scA[u >> 2] >> (8 * (u & 3))) & 0xff);
-          const float fb = e8m0_to_f32((f.scB[u >> 2] >> (8 * (u & 3))) & 0xff);
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            uint2 bf = xf[(u * NT + nt) * 32];
-            float2 sx = *reinterpret_cast<const float2*>(sxp + (u * NT + nt) * 8);
-            float d[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_e4m3(d, a0, a1, a2, a3, bf.x, bf.y);
-            acc[nt][0] = fmaf(d[0], fa * sx.x, acc[nt][0]);
-            acc[nt][1] = fmaf(d[1], fa * sx.y, acc[nt][1]);
-            acc[nt][2] = fmaf(d[2], fb * sx.x, acc[nt][2]);
-            acc[nt][3] = fmaf(d[3], fb * sx.y, acc[nt][3]);
-          }
-        }
+      for (int nt = 0; nt < NT; ++nt) {
+        uint2 bf = xf[(u * NT + nt) * 32];
+        float2 sx = *reinterpret_cast<const float2*>(sxp + (u * NT + nt) * 8);
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_e4m3(d, a0, a1, a2, a3, bf.x, bf.y);
+        acc[nt][0] = fmaf(d[0], fa * sx.x, acc[nt][0]);
+        acc[nt][1] = fmaf(d[1], fa * sx.y, acc[nt][1]);
+        acc[nt][2] = fmaf(d[2], fb * sx.x, acc[nt][2]);
+        acc[nt][3] = fmaf(d[3], fb * sx.y, acc[nt][3]);
       }
     }
   };
 
   const int tstride = gridDim.x * kGroups;
-  int tile = blockIdx.x * kGroups + group, bi = 0, step = 0;
-  bool have = tile < ntiles;
-  if (have) issue(buf0, tile, 0);
+  int tile = blockIdx.x * kGroups + group, bi = 0;
+  bool have = !is_epi && tile < ntiles;
+  if (have) {
+    const BatchAddr a0 = locate(tile, 0);
+#pragma unroll
+    for (int u = 0; u < U; ++u) load_unit(buf, a0, u);
+#pragma unroll
+    for (int q = 0; q < U / 4; ++q) load_scales(buf, a0, q);
+  }
 
   // ---- activations -> B fragments in shared memory, while the first weight loads are in flight ----
   if constexpr (MODE != VQK_MODE_W8A16) pdl_wait();  // the quantized activations come from the kernel before
@@ -332,113 +354,135 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   __syncthreads();
 
 
+  // ---- streaming warps ------------------------------------------------------------------------
+  int tcount = 0;  // tiles this group has finished
   while (have) {
     int ntile = tile, nbi = bi + 1;
     if (nbi == nb) { nbi = 0; ntile = tile + tstride; }
     const bool nhave = ntile < ntiles;
-    if ((step & 1) == 0) {
-      if (nhave) issue(buf1, ntile, nbi);
-      consume(buf0, bi);
-    } else {
-      if (nhave) issue(buf0, ntile, nbi);
-      consume(buf1, bi);
+    // One set of registers, refilled unit by unit: as soon as a unit's MMAs have read it, the same
+    // registers fetch that unit of the NEXT batch (also across tile boundaries), so U units per lane
+    // are in flight all the time and the HBM stream of a warp never waits for its own arithmetic.
+    const BatchAddr nxt = locate(nhave ? ntile : tile, nhave ? nbi : bi);
+    const int u0 = ubeg + bi * U;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      consume_unit(buf, u0, u);
+      if (nhave) load_unit(buf, nxt, u);
+      if constexpr (MX)
+        if ((u & 3) == 3 && nhave) load_scales(buf, nxt, u >> 2);
     }
-    ++step;
-    const int row0 = tile * 16;
     const bool tile_done = (bi == nb - 1);
     tile = ntile; bi = nbi; have = nhave;
     if (!tile_done) continue;
 
-    // ---- cross-warp (split-K) reduction through shared memory --------------------------
+    // ---- park the split-K partial sums for the epilogue warp and go on -----------------------
+    const int par = tcount & 1;
+    // (the buffer's previous contents, two tiles back, have been read: normally long ago)
+    if (!mbar_wait_warp(&freeb[group * 2 + par], (((uint32_t)tcount >> 1) & 1u) ^ 1u, abort_flag)) break;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      acc_t* r = myred + nt * 128;
+      acc_t* r = myred + par * kRedBuf + nt * 128;
       r[(2 * t) * 16 + g] = acc[nt][0];
       r[(2 * t + 1) * 16 + g] = acc[nt][1];
       r[(2 * t) * 16 + g + 8] = acc[nt][2];
       r[(2 * t + 1) * 16 + g + 8] = acc[nt][3];
       acc[nt][0] = 0; acc[nt][1] = 0; acc[nt][2] = 0; acc[nt][3] = 0;
     }
-    asm volatile("bar.sync %0, 128;" ::"r"(group + 1));
+    mbar_arrive(&fullb[group * 2 + par]);
+    ++tcount;
+  }
 
-    // ---- epilogue: thread e -> (vocab row row0 + er, batch column nt*8 + ec) ------------
-    const int row = row0 + er;
-    const bool row_ok = row < V;
-    float rs = 1.f, bias = 0.f;
-    if (row_ok) {
-      if constexpr (MODE == VQK_MODE_W8A16 || MODE == VQK_MODE_FP8)
-        rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[row]);
-      if constexpr (MODE == VQK_MODE_W8A8) rs = reinterpret_cast<const float*>(p.wscale)[row];
-      if (p.bias) bias = __half2float(p.bias[row]);
-    }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int b = nt * 8 + ec;
-      bool pass = false;  // a top-k column's logit that beats the last entry of the slice's list
-      float l = 0.f;
-      if (row_ok && b < B) {
-        acc_t s = gred[0 * NT * 128 + nt * 128 + e] + gred[1 * NT * 128 + nt * 128 + e] +
-                  gred[2 * NT * 128 + nt * 128 + e] + gred[3 * NT * 128 + nt * 128 + e];
-        float v;
-        if constexpr (MODE == VQK_MODE_W8A8) v = ((float)s * rs) * xs_w8a8;   // _kernels.py:471, left to right
-        else if constexpr (MX) v = s;
-        else v = s * rs;
-        __half h = __float2half_rn(v);
-        if (p.bias) h = __float2half_rn(__half2float(h) + bias);
-        h = logit_post_ops(h, p.soft_cap, p.out_scale);
-        if (p.logits) p.logits[(long long)b * p.ld_logits + row] = h;
-        if (p.do_sample) {
-          const RowMeta m = meta[b];
-          l = __half2float(h);
-          if (m.flags & ROW_CAND) {
-            p.cand_logits[(long long)b * p.ld_cand + row] = h;
-            pass = l > slist[b * kListLen + kListM].v;
-          } else {
-            float sc = l;
-            const int tok = row;  // local id; offset added by the consumer
-            if (!(m.flags & ROW_GREEDY)) {
-              sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(row + p.sp.vocab_offset));
-              if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
+  // ---- epilogue warps: lane -> vocab row (lane & 15) of the tile, batch columns (lane >> 4) + 2j ----
+  if (is_epi) {
+    const int gi = warp - kStreamWarps;
+    const int er = lane & 15, eh = lane >> 4;
+    Cand* slist = slist_all + (size_t)gi * NT * 8 * kListLen;
+    Cand* win = swin + (size_t)gi * NT * 8 * 16;
+    int rnd = 0;
+    for (int etile = blockIdx.x * kGroups + gi; etile < ntiles; etile += tstride, ++rnd) {
+      const int row = etile * 16 + er;
+      const bool row_ok = row < V;
+      // the row's scale (and bias), in flight while the partial sums are awaited
+      float rs = 1.f, bias = 0.f;
+      if (row_ok) {
+        if constexpr (MODE == VQK_MODE_W8A16 || MODE == VQK_MODE_FP8)
+          rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[row]);
+        if constexpr (MODE == VQK_MODE_W8A8) rs = reinterpret_cast<const float*>(p.wscale)[row];
+        if (p.bias) bias = __half2float(p.bias[row]);
+      }
+      const int par = rnd & 1;
+      if (!mbar_wait_warp(&fullb[gi * 2 + par], ((uint32_t)rnd >> 1) & 1u, abort_flag)) break;
+      const acc_t* gred = red + par * kRedBuf + (size_t)(gi * 4) * NT * 128;
+      for (int b0 = 0; b0 < B; b0 += 2) {  // two columns per pass, one per half warp
+        const int b = b0 + eh;
+        bool pass = false;  // a top-k column's logit that beats the last entry of the slice's list
+        float l = 0.f;
+        if (row_ok && b < B) {
+          const acc_t* q = gred + (b >> 3) * 128 + (b & 7) * 16 + er;
+          acc_t sum = q[0 * NT * 128] + q[1 * NT * 128] + q[2 * NT * 128] + q[3 * NT * 128];
+          float v;
+          if constexpr (MODE == VQK_MODE_W8A8) v = ((float)sum * rs) * xs_w8a8;   // _kernels.py:471, left to right
+          else if constexpr (MX) v = sum;
+          else v = sum * rs;
+          __half h = __float2half_rn(v);
+          if (p.bias) h = __float2half_rn(__half2float(h) + bias);
+          h = logit_post_ops(h, p.soft_cap, p.out_scale);
+          if (p.logits) p.logits[(long long)b * p.ld_logits + row] = h;
+          if (p.do_sample) {
+            const RowMeta m = meta[b];
+            l = __half2float(h);
+            if (m.flags & ROW_CAND) {
+              p.cand_logits[(long long)b * p.ld_cand + row] = h;
+              pass = l > slist[b * kListLen + kListM].v;
+            } else {
+              float sc = l;
+              if (!(m.flags & ROW_GREEDY)) {
+                sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(row + p.sp.vocab_offset));
+                if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
+              }
+              const Cand w = win[b * 16 + er];  // this lane's own entry: local token id, offset added by the consumer
+              if (better(sc, row, w.v, w.t)) win[b * 16 + er] = Cand{sc, row};
             }
-            if (better(sc, tok, bs[nt], bt[nt])) { bs[nt] = sc; bt[nt] = tok; }
+          }
+        }
+        if (p.do_sample) {
+          // The slice's kListLen largest logits per column live in shared memory.  Once the list has
+          // warmed up hardly any logit beats its last entry, so this is one vote per tile; the few
+          // that do go in one after the other.
+          unsigned mask = __ballot_sync(0xffffffffu, pass);
+          while (mask) {
+            const int src = __ffs(mask) - 1;
+            mask &= mask - 1;
+            if (lane == src) list_insert(slist + b * kListLen, kListLen, l, row);
+            __syncwarp();
           }
         }
       }
-      if (p.do_sample) {
-        // The slice's kListLen largest logits per column live in shared memory.  Once the list has
-        // warmed up hardly any logit beats its last entry, so this is one vote per tile; the few
-        // that do go in one after the other (a warp holds two columns, sixteen rows each).
-        unsigned mask = __ballot_sync(0xffffffffu, pass);
-        while (mask) {
-          const int src = __ffs(mask) - 1;
-          mask &= mask - 1;
-          if (lane == src) list_insert(slist + b * kListLen, kListLen, l, row);
-          __syncwarp();
-        }
-      }
+      mbar_arrive(&freeb[gi * 2 + par]);
     }
-    asm volatile("bar.sync %0, 128;" ::"r"(group + 1));
   }
+  __syncthreads();
 
   dbg_stamp(p, 1);
-  // ---- per-slice sampler results: reduce over the 16 row-threads of each column ----------
+  // ---- per-slice sampler results: warp w < 4 writes group w's, two columns per pass --------------
   if (p.do_sample) {
-    const int slice = blockIdx.x * kGroups + group;
-    __syncwarp();
+    if (warp < kGroups) {
+      const int slice = blockIdx.x * kGroups + warp;
+      const Cand* slist = slist_all + (size_t)warp * NT * 8 * kListLen;
+      const Cand* win = swin + (size_t)warp * NT * 8 * 16;
+      for (int b0 = 0; b0 < B; b0 += 2) {
+        const int b = b0 + (lane >> 4);
+        Cand w{-INFINITY, 0x7fffffff};
+        if (b < B) w = win[b * 16 + (lane & 15)];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      float s = bs[nt];
-      int tk = bt[nt];
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) {
-        float s2 = __shfl_xor_sync(0xffffffffu, s, o);
-        int t2 = __shfl_xor_sync(0xffffffffu, tk, o);
-        if (better(s2, t2, s, tk)) { s = s2; tk = t2; }
-      }
-      const int b = nt * 8 + ec;
-      if (b < B) {
-        const long long o = (long long)b * p.nslices + slice;
-        if (er == 0) {
+        for (int o = 8; o > 0; o >>= 1) {
+          const float s2 = __shfl_xor_sync(0xffffffffu, w.v, o);
+          const int t2 = __shfl_xor_sync(0xffffffffu, w.t, o);
+          if (better(s2, t2, w.v, w.t)) { w.v = s2; w.t = t2; }
+        }
+        if (b < B && (lane & 15) == 0) {
+          const long long o = (long long)b * p.nslices + slice;
           if (p.lists) {
             SliceList rec;
 #pragma unroll
@@ -451,8 +495,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
             p.lists[o] = rec;
           }
           p.slice_max[o] = slist[b * kListLen].v;
-          p.part_score[o] = s;
-          p.part_token[o] = tk;
+          p.part_score[o] = w.v;
+          p.part_token[o] = w.t;
         }
       }
     }
@@ -460,6 +504,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
     if (p.fuse_tail) lm_head_tail(p, meta, smem, stream_smem_total(MODE, p.K, NT, B));
   }
 }
+
+int stream_error_flag() { return read_stream_error(); }
+int stream_error_clear() { return clear_stream_error(); }
 
 // ---- host launch -------------------------------------------------------------------------
 template <int MODE, int NT, int U, bool EVEN>
@@ -494,6 +541,9 @@ static int launch_stream_u(const LmHeadParams& p, int grid, cudaStream_t st) {
     if (whole && per % 8 == 0) return launch_stream<MODE, NT, 8, true>(p, grid, st);
     return launch_stream<MODE, NT, 8, false>(p, grid, st);
   } else {
+    // six units (192 B per lane) in flight where the shape allows: 96 KB per SM (VQK_STREAM_U=4: A/B runs)
+    static const bool u6 = [] { const char* e = getenv("VQK_STREAM_U"); return !(e && atoi(e) == 4); }();
+    if (u6 && whole && per % 6 == 0) return launch_stream<MODE, NT, 6, true>(p, grid, st);
     if (whole && per % 4 == 0) return launch_stream<MODE, NT, 4, true>(p, grid, st);
     return launch_stream<MODE, NT, 4, false>(p, grid, st);
   }

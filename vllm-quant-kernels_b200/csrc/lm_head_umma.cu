@@ -164,8 +164,7 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
     }
   } else {
     pdl_wait();  // W8A8: the activation scale comes from the kernel before
-    umma_epilogue<INT8 ? 1 : 0, BN, NI>(p, warp, lane, tmem_base, tfull, tempty, abort_flag, meta, sstate, sched_interleaved(V),
-                                        reinterpret_cast<Cand*>(sstate + (size_t)12 * BN), nullptr);
+    umma_epilogue<INT8 ? 1 : 0, BN, NI>(p, warp, lane, tmem_base, tfull, tempty, abort_flag, meta, sstate, sched_interleaved(V));
   }
 
   tc_fence_before();
@@ -174,10 +173,7 @@ k_lm_head_umma(const LmHeadParams p, const __grid_constant__ CUtensorMap mapA, c
     tc_fence_after();
     tmem_dealloc(tmem_base, TCOLS);
   }
-  // decode-sized batches: the last CTA of the grid resolves the rows; the stage ring is free by now
-  if (p.fuse_tail) lm_head_tail(p, meta, smem, (size_t)NI * S * geo.stage_bytes);
 }
-
 
 // ---- host side ------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -54,13 +54,15 @@ struct PeerRowResult {
 
 // One row, one warp.  This rank's record is (score, token, n, flags) with candidate i = cand(i)
 // (raw logit, GLOBAL token).  The union of all ranks' candidates lands in mv / mt (kMergeCap each).
+// `step`: this step's number for the row (the stored counter + 1) when the caller fetched the
+// counter ahead of time, 0 to fetch it here.
 template <typename CandAt>
 __device__ inline PeerRowResult peer_exchange_row(const PeerTable& pt, int b, float score, int token, int n, int flags,
-                                                  CandAt cand, float* mv, int* mt, int lane) {
+                                                  CandAt cand, float* mv, int* mt, int lane, unsigned int step = 0) {
   const int G = pt.G;
-  unsigned int step = 0;
   if (lane == 0) {
-    step = pt.steps[b] + 1u;
+    if (step == 0) step = pt.steps[b] + 1u;
+    if (step == 0) step = 2u;  // the counter wrapped: keep the parity sequence, skip the reserved 0
     pt.steps[b] = step;
   }
   step = __shfl_sync(0xffffffffu, step, 0);
@@ -153,7 +155,8 @@ __device__ inline PeerRowResult peer_exchange_row(const PeerTable& pt, int b, fl
     unsigned long long* slot = const_cast<unsigned long long*>(mine) + ((parity_off + g) * pt.max_rows + b) * kWireWords;
     for (int i = lane; i < cnt; i += 32) slot[i] = 0ull;
   }
-  __threadfence_system();
+  // (no fence: a peer writes these words again only after it has read this rank's record of the NEXT
+  // step, which a later launch sends; the end of this launch puts the zeroes in memory before that)
   __syncwarp();
   return r;
 }

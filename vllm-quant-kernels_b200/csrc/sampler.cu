@@ -354,14 +354,21 @@ __device__ float smem_kth_largest(const float* v, int n, int k, unsigned int* hi
 // Sharded step: the record k_select just wrote for row b travels to every rank and the shards are
 // merged, by the first warp of the row's CTA (peer_exchange.cuh).  `buf` is block shared memory of
 // at least kTailWarpBytes.
-__device__ void select_exchange_row(const SelectParams& p, int b, const RowMeta& m, uint8_t* buf) {
-  __syncthreads();  // the record of this row is complete (written by this block)
+struct SelectExchange {  // in shared memory: what the exchange needs of the kernel's parameters
+  PeerTable peer;
+  RowMeta m;
+  const uint8_t* records;
+  long long* tokens;
+  float* scores;
+};
+static __device__ __noinline__ void select_exchange_row(const SelectExchange& x, int b, uint8_t* buf) {
+  __syncthreads();  // the record of this row is complete (written by this block), and so is x
   if (threadIdx.x >= 32) return;
-  const uint8_t* rec = p.records + (size_t)b * VQK_RECORD_BYTES;
+  const uint8_t* rec = x.records + (size_t)b * VQK_RECORD_BYTES;
   const RecordHeader h = *reinterpret_cast<const RecordHeader*>(rec);
   const Cand* cd = reinterpret_cast<const Cand*>(rec + sizeof(RecordHeader));
-  tail_exchange_row(p.peer, m, b, h.score, h.token, h.n, h.flags, [&](int i) { return cd[i]; }, buf,
-                    (int)threadIdx.x, p.tokens, p.scores);
+  tail_exchange_row(x.peer, x.m, b, h.score, h.token, h.n, h.flags, [&](int i) { return cd[i]; }, buf,
+                    (int)threadIdx.x, x.tokens, x.scores);
 }
 
 // ---- pass 2: one cluster per row -----------------------------------------------------------------
@@ -399,7 +406,15 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   __shared__ int s_nrec;
   __shared__ FullRowScratch s_full;
   __shared__ __align__(16) uint8_t s_xbuf[kTailWarpBytes];  // sharded step: scratch of the record exchange
+  __shared__ SelectExchange s_x;
   const bool exchange = p.peer.G > 0;
+  if (exchange && tid == 0) {
+    s_x.peer = p.peer;
+    s_x.m = m;
+    s_x.records = p.records;
+    s_x.tokens = p.tokens;
+    s_x.scores = p.scores;
+  }
 
   if (!(m.flags & ROW_CAND)) {
     // row already reduced to per-slice winners: merge them (rank 0 only, no cluster traffic)
@@ -417,7 +432,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       if (p.tokens) p.tokens[b] = tok;
       if (p.scores) p.scores[b] = best.s;
     }
-    if (exchange) select_exchange_row(p, b, m, s_xbuf);
+    if (exchange) select_exchange_row(s_x, b, s_xbuf);
     return;
   }
 
@@ -436,7 +451,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_NEEDS_ROW);
       if (p.tokens) p.tokens[b] = -1;
     }
-    if (exchange) select_exchange_row(p, b, m, s_xbuf);
+    if (exchange) select_exchange_row(s_x, b, s_xbuf);
     return;
   }
 
@@ -522,7 +537,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       write_header(p.records, b, -INFINITY, -1, 0, VQK_RECORD_FLAG_OVERFLOW);
       if (p.tokens) p.tokens[b] = -1;
     }
-    if (exchange) select_exchange_row(p, b, m, s_xbuf);
+    if (exchange) select_exchange_row(s_x, b, s_xbuf);
     return;
   }
 
@@ -557,7 +572,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
       if (p.scores) p.scores[b] = w.s;
     }
   }
-  if (exchange) select_exchange_row(p, b, m, s_xbuf);
+  if (exchange) select_exchange_row(s_x, b, s_xbuf);
 }
 
 // ---- merge of gathered shard records -----------------------------------------------------------

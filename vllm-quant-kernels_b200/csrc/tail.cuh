@@ -166,7 +166,21 @@ static __device__ __noinline__ int warp_topk_inplace(float* v, int* t, int n, in
   int low = 1;
   for (int i = lane; i < n; i += 32) low &= ((__float_as_uint(v[i]) & 0x1fffu) == 0);
   low = __all_sync(0xffffffffu, low);
-  const uint32_t tk = warp_kth_largest_key([&](int i) { return f32_key(v[i]); }, n, K, 31, low ? 13 : 0, lane);
+  float thr;  // the K-th largest value; entries >= it survive (float compare: -0 ties with +0)
+  if (low && n <= 512) {  // the usual case: fp16 logits, a few per lane - select on registers, 16-bit keys
+    uint32_t key[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) key[j] = j * 32 + lane < n ? h16_key(v[j * 32 + lane]) : 0u;
+    int fin = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) fin += (key[j] >= kKeyLowestFinite);
+    fin = __reduce_add_sync(0xffffffffu, fin);
+    // (-inf entries can only come from an all -inf shard; with fewer than K finite values all of them survive)
+    const uint32_t k16 = fin >= K ? warp_kth_largest_reg(key, K) : kKeyLowestFinite;
+    thr = h16_key_to_float(k16);
+  } else {
+    thr = key_f32(warp_kth_largest_key([&](int i) { return f32_key(v[i]); }, n, K, 31, low ? 13 : 0, lane));
+  }
   const unsigned lt = (1u << lane) - 1u;
   int kept = 0;
 #pragma unroll 1
@@ -175,7 +189,7 @@ static __device__ __noinline__ int warp_topk_inplace(float* v, int* t, int n, in
     float vi = 0.f;
     int ti = 0;
     bool keep = false;
-    if (i < n) { vi = v[i]; ti = t[i]; keep = f32_key(vi) >= tk; }
+    if (i < n) { vi = v[i]; ti = t[i]; keep = vi >= thr; }
     const unsigned mask = __ballot_sync(0xffffffffu, keep);  // every lane has read before anyone writes
     if (keep) { const int pos = kept + __popc(mask & lt); v[pos] = vi; t[pos] = ti; }
     kept += __popc(mask);
@@ -186,9 +200,12 @@ static __device__ __noinline__ int warp_topk_inplace(float* v, int* t, int n, in
 
 // Top-p over the n <= kTailSurvCap top-k survivors, then the Gumbel argmax: the arithmetic of
 // resolve_candidates (sampler.cu), so both paths pick the same token with the same score.
-static __device__ __noinline__ void warp_topp_gumbel(const float* cv, const int* ct, int n, float T, float top_p, int seed,
-                                              float* y, unsigned long long* w, unsigned char* alive, int lane,
-                                              float* s_out, int* t_out) {
+struct TailWinner {
+  float s;
+  int t;
+};
+static __device__ __noinline__ TailWinner warp_topp_gumbel(const float* cv, const int* ct, int n, float T, float top_p, int seed,
+                                                           float* y, unsigned long long* w, unsigned char* alive, int lane) {
 #pragma unroll 1
   for (int i = lane; i < n; i += 32) { y[i] = cv[i] / T; alive[i] = 1; }
   __syncwarp();
@@ -229,14 +246,13 @@ static __device__ __noinline__ void warp_topp_gumbel(const float* cv, const int*
     if (better(sc, ct[i], s, t)) { s = sc; t = ct[i]; }
   }
   warp_best_pair(s, t);
-  *s_out = s;
-  *t_out = t;
+  return TailWinner{s, t};
 }
 
 // The same for n <= 64 survivors (the usual case: k + ties), held two per lane in registers: the
 // mass above each survivor is summed over shuffles, the two Gumbel draws of a lane run side by side.
-static __device__ __noinline__ void warp_topp_gumbel64(const float* cv, const int* ct, int n, float T, float top_p, int seed,
-                                                       int lane, float* s_out, int* t_out) {
+static __device__ __noinline__ TailWinner warp_topp_gumbel64(const float* cv, const int* ct, int n, float T, float top_p,
+                                                             int seed, int lane) {
   const bool h0 = lane < n, h1 = lane + 32 < n;
   const float y0 = h0 ? cv[lane] / T : -INFINITY, y1 = h1 ? cv[lane + 32] / T : -INFINITY;
   const int t0 = h0 ? ct[lane] : 0x7fffffff, t1 = h1 ? ct[lane + 32] : 0x7fffffff;
@@ -270,8 +286,7 @@ static __device__ __noinline__ void warp_topp_gumbel64(const float* cv, const in
   const float s1 = a1 ? y1 + g1 : -INFINITY;
   if (a1 && better(s1, t1, s, t)) { s = s1; t = t1; }
   warp_best_pair(s, t);
-  *s_out = s;
-  *t_out = t;
+  return TailWinner{s, t};
 }
 
 // Sharded step: exchange this rank's record of row b and merge the shards.  Whole warp; writes the
@@ -279,10 +294,10 @@ static __device__ __noinline__ void warp_topp_gumbel64(const float* cv, const in
 template <typename CandAt>
 __device__ inline void tail_exchange_row(const PeerTable& pt, const RowMeta& m, int b, float score, int token, int n,
                                          int flags, CandAt cand, uint8_t* scratch, int lane, long long* tokens,
-                                         float* scores) {
+                                         float* scores, unsigned int step = 0) {
   float* mv = reinterpret_cast<float*>(scratch + kTailOffMv);
   int* mt = reinterpret_cast<int*>(scratch + kTailOffMt);
-  const PeerRowResult r = peer_exchange_row(pt, b, score, token, n, flags, cand, mv, mt, lane);
+  const PeerRowResult r = peer_exchange_row(pt, b, score, token, n, flags, cand, mv, mt, lane, step);
   float s = -INFINITY;
   int t = -1;
   if (!r.late && !r.bad) {
@@ -292,11 +307,15 @@ __device__ inline void tail_exchange_row(const PeerTable& pt, const RowMeta& m, 
     } else {
       __syncwarp();
       const int kept = warp_topk_inplace(mv, mt, r.total, m.top_k, lane);
-      if (kept <= 64)
-        warp_topp_gumbel64(mv, mt, kept, m.T, m.top_p, m.seed, lane, &s, &t);
-      else if (kept <= kTailSurvCap)
-        warp_topp_gumbel(mv, mt, kept, m.T, m.top_p, m.seed, reinterpret_cast<float*>(scratch + kTailOffY),
-                         reinterpret_cast<unsigned long long*>(scratch + kTailOffW), scratch + kTailOffAlive, lane, &s, &t);
+      if (kept <= kTailSurvCap) {
+        const TailWinner w = kept <= 64 ? warp_topp_gumbel64(mv, mt, kept, m.T, m.top_p, m.seed, lane)
+                                        : warp_topp_gumbel(mv, mt, kept, m.T, m.top_p, m.seed,
+                                                           reinterpret_cast<float*>(scratch + kTailOffY),
+                                                           reinterpret_cast<unsigned long long*>(scratch + kTailOffW),
+                                                           scratch + kTailOffAlive, lane);
+        s = w.s;
+        t = w.t;
+      }
     }
   }
   if (lane == 0) {
@@ -324,12 +343,21 @@ struct TailArgs {
 // One row, one warp.  Returns 1 when the row is done, 0 when it has to go to the full-row kernel,
 // 2 when it is resolved as far as this shard goes and its record (survivors in cv / ct, count in
 // *nsv_out, or the winner in *win_s / *win_t) still has to be exchanged.
-static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, const RowMeta& m, int b, uint8_t* scratch, int lane,
-                                                    bool exchange, int* nsv_out, float* win_s, int* win_t) {
+struct TailRowResult {
+  int status;  // 1 done, 0 to the full-row kernel, 2 record to be exchanged
+  int nsv;     // survivors in cv / ct (status 2, top-k rows)
+  float win_s; // the shard's winner (status 2, rows without top-k / top-p)
+  int win_t;
+};
+// (`a` and `m` live in SHARED memory: in a kernel that takes nearly all of the SM's shared memory
+// the L1 is too small to be relied on for stack traffic, and a single warp pays an L2 round trip
+// for every miss)
+static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a, const RowMeta& m, int b, uint8_t* scratch,
+                                                              int lane, bool exchange) {
+  TailRowResult res{0, 0, -INFINITY, 0x7fffffff};
   const int nsl = a.nslices;
   const long long voff = a.sp.vocab_offset;
   const unsigned lt = (1u << lane) - 1u;
-  *nsv_out = 0;
   if (!(m.flags & ROW_CAND)) {
     // per-slice winners -> row winner (the same merge k_select does for these rows)
     float s = -INFINITY;
@@ -342,17 +370,17 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, const Row
     }
     warp_best_pair(s, t);
     const long long tok = (long long)t + voff;
-    *win_s = s;
-    *win_t = (int)tok;
-    if (exchange) return 2;
-    if (lane == 0) {
+    res.win_s = s;
+    res.win_t = (int)tok;
+    res.status = exchange ? 2 : 1;
+    if (!exchange && lane == 0) {
       tail_write_header(a.records, b, s, (int)tok, 0, 0);
       if (a.tokens) a.tokens[b] = tok;
       if (a.scores) a.scores[b] = s;
     }
-    return 1;
+    return res;
   }
-  if (!a.lists || m.top_k <= 0 || m.top_k > kTailMaxK || nsl > kTailMaxSlices || (nsl & 3)) return 0;
+  if (!a.lists || m.top_k <= 0 || m.top_k > kTailMaxK || nsl > kTailMaxSlices || (nsl & 3)) return res;
 
   uint16_t* qsel = reinterpret_cast<uint16_t*>(scratch + kTailOffQuads);
   uint2* st = reinterpret_cast<uint2*>(scratch + kTailOffStage);
@@ -390,7 +418,7 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, const Row
     if (hit && pos < kTailQuadCap) qsel[pos] = (uint16_t)(j * 32 + lane);
     nsel += __popc(mask);
   }
-  if (nsel > kTailQuadCap) return 0;
+  if (nsel > kTailQuadCap) return res;
   __syncwarp();
   if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[6] = t_; }
   // 4. trip two: the list records of their slices (two 16-byte loads each, up to kTailRecRegs per lane
@@ -430,7 +458,7 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, const Row
       if (lane >= o) incl += t2;
     }
     const int batch = __shfl_sync(0xffffffffu, incl, 31);
-    if (ne + batch > kTailStageCap) return 0;
+    if (ne + batch > kTailStageCap) return res;
     int wpos = ne + incl - mine_n;
 #pragma unroll
     for (int r = 0; r < kTailRecRegs; ++r) {
@@ -458,7 +486,7 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, const Row
     }
   }
   // 6. the proof: no slice we looked at hides a value >= t_k (the others have maximum < tau0 <= t_k)
-  if (wkey >= tk) return 0;
+  if (wkey >= tk) return res;
   if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[10] = t_; }
   // 7. survivors (>= t_k, ties kept), with their GLOBAL token ids
   int nsv = 0;
@@ -475,39 +503,79 @@ static __device__ __noinline__ int tail_resolve_row(const TailArgs& a, const Row
     }
     nsv += __popc(mask);
   }
-  if (nsv > kTailSurvCap) return 0;
+  if (nsv > kTailSurvCap) return res;
   __syncwarp();
-  *nsv_out = nsv;
-  if (exchange) return nsv > VQK_RECORD_CAP ? 0 : 2;  // (the full-row kernel reports an overflowing record)
+  res.nsv = nsv;
+  if (exchange) {
+    res.status = nsv > VQK_RECORD_CAP ? 0 : 2;  // (the full-row kernel reports an overflowing record)
+    return res;
+  }
   if (a.records) {  // shard record: the local top-k survivors; top-p needs the union of the shards
     Cand* out = reinterpret_cast<Cand*>(a.records + (size_t)b * VQK_RECORD_BYTES + sizeof(RecordHeader));
     for (int i = lane; i < nsv && i < VQK_RECORD_CAP; i += 32) out[i] = Cand{cv[i], ct[i]};
     if (lane == 0)
       tail_write_header(a.records, b, -INFINITY, -1, min(nsv, VQK_RECORD_CAP), nsv > VQK_RECORD_CAP ? VQK_RECORD_FLAG_OVERFLOW : 0);
   }
-  if (!a.single_shard) return 1;
+  res.status = 1;
+  if (!a.single_shard) return res;
   if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[11] = t_; }
   // 8. top-p over the survivors, then the Gumbel argmax
-  float s;
-  int t;
-  if (nsv <= 64)
-    warp_topp_gumbel64(cv, ct, nsv, m.T, m.top_p, m.seed, lane, &s, &t);
-  else
-    warp_topp_gumbel(cv, ct, nsv, m.T, m.top_p, m.seed, reinterpret_cast<float*>(scratch + kTailOffY),
-                     reinterpret_cast<unsigned long long*>(scratch + kTailOffW), scratch + kTailOffAlive, lane, &s, &t);
+  const TailWinner w = nsv <= 64 ? warp_topp_gumbel64(cv, ct, nsv, m.T, m.top_p, m.seed, lane)
+                                 : warp_topp_gumbel(cv, ct, nsv, m.T, m.top_p, m.seed,
+                                                    reinterpret_cast<float*>(scratch + kTailOffY),
+                                                    reinterpret_cast<unsigned long long*>(scratch + kTailOffW),
+                                                    scratch + kTailOffAlive, lane);
   if (lane == 0) {
-    if (a.tokens) a.tokens[b] = t;
-    if (a.scores) a.scores[b] = s;
+    if (a.tokens) a.tokens[b] = w.t;
+    if (a.scores) a.scores[b] = w.s;
   }
-  return 1;
+  return res;
+}
+
+// Everything the rows' resolution needs, in SHARED memory of the CTA that runs it (filled by one
+// thread from the kernel's parameters), so that the code below can live in a function of its own:
+// inlined into the lm_head kernels it cost them registers and instruction-cache room for nothing
+// (147 of the 148 CTAs never run it).
+struct TailShared {
+  TailArgs a;
+  PeerTable peer;
+  RowMeta meta[kTailMaxBatch];      // a copy outside the scratch, which may overlay the kernel's own
+  unsigned int step[kTailMaxBatch];  // sharded step: the rows' step numbers, fetched ahead of the exchange
+  int* row_flag;
+  int B, mode;
+};
+
+static __device__ __noinline__ void lm_head_tail_rows(const TailShared& sh, uint8_t* scratch, int nw) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= nw) return;
+  uint8_t* mine = scratch + (size_t)warp * kTailWarpBytes;
+  const bool exchange = sh.peer.G > 0;
+  for (int b = warp; b < sh.B; b += nw) {
+    TailRowResult rr{0, 0, 0.f, 0};
+    if (sh.mode == 1) rr = tail_resolve_row(sh.a, sh.meta[b], b, mine, lane, exchange);  // 2: A/B runs, every row to the full-row kernel
+    int r = rr.status;
+    if (r == 2) {
+      const float* cv = reinterpret_cast<const float*>(mine + kTailOffCv);
+      const int* ct = reinterpret_cast<const int*>(mine + kTailOffCt);
+      if (sh.meta[b].flags & ROW_CAND)
+        tail_exchange_row(sh.peer, sh.meta[b], b, -INFINITY, -1, rr.nsv, 0, [&](int i) { return Cand{cv[i], ct[i]}; }, mine, lane,
+                          sh.a.tokens, sh.a.scores, sh.step[b]);
+      else
+        tail_exchange_row(sh.peer, sh.meta[b], b, rr.win_s, rr.win_t, 0, 0, [](int) { return Cand{0.f, 0}; }, mine, lane,
+                          sh.a.tokens, sh.a.scores, sh.step[b]);
+      r = 1;
+    }
+    if (lane == 0) sh.row_flag[b] = r ? 0 : 1;
+    __syncwarp();
+  }
 }
 
 // Called by every thread of every CTA once its slice results are written.  `scratch` is shared
 // memory of the CTA that is no longer in use, `scratch_bytes` of it (at least kTailWarpBytes).
 // `meta`: the rows' sampling parameters as the kernel decoded them at its start (shared memory).
-__device__ inline void lm_head_tail(const LmHeadParams& p, const RowMeta* meta, uint8_t* scratch, size_t scratch_bytes) {
+__device__ __forceinline__ void lm_head_tail(const LmHeadParams& p, const RowMeta* meta, uint8_t* scratch, size_t scratch_bytes) {
   __shared__ int s_last;
-  __shared__ RowMeta s_meta[kTailMaxBatch];  // a copy outside the scratch, which may overlay `meta`
+  __shared__ TailShared s_tail;
   __syncthreads();  // every thread's slice results are written ...
   if (threadIdx.x == 0) {
     __threadfence();  // ... and visible device-wide before the ticket is taken (the fence is cumulative over the barrier)
@@ -517,38 +585,26 @@ __device__ inline void lm_head_tail(const LmHeadParams& p, const RowMeta* meta, 
   __syncthreads();
   if (!s_last) return;
   dbg_stamp(p, 3);
-  if (threadIdx.x < p.B && threadIdx.x < kTailMaxBatch) s_meta[threadIdx.x] = meta[threadIdx.x];
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int nw = min((int)(blockDim.x >> 5), kTailMaxWarps);
-  nw = min(nw, (int)(scratch_bytes / kTailWarpBytes));
-  if (warp < nw) {
-    uint8_t* mine = scratch + (size_t)warp * kTailWarpBytes;
+  if (threadIdx.x < p.B && threadIdx.x < kTailMaxBatch) {
+    s_tail.meta[threadIdx.x] = meta[threadIdx.x];
+    s_tail.step[threadIdx.x] = p.peer.G > 0 ? p.peer.steps[threadIdx.x] + 1u : 0u;
+  }
+  if (threadIdx.x == 0) {
     TailArgs a;
     a.sp = p.sp; a.slice_max = p.slice_max; a.part_score = p.part_score; a.part_token = p.part_token;
     a.lists = p.lists; a.nslices = p.nslices; a.tokens = p.tokens; a.scores = p.scores;
     a.records = p.records; a.single_shard = p.single_shard;
     a.dbg = p.dbg ? p.dbg + (size_t)blockIdx.x * 16 : nullptr;
-    const bool exchange = p.peer.G > 0;
-    for (int b = warp; b < p.B; b += nw) {
-      int nsv = 0, wt = 0;
-      float ws = 0.f;
-      int r = 0;
-      const RowMeta m = s_meta[b];
-      if (p.fuse_tail == 1) r = tail_resolve_row(a, m, b, mine, lane, exchange, &nsv, &ws, &wt);  // 2: A/B runs, every row to the full-row kernel
-      if (r == 2) {
-        const float* cv = reinterpret_cast<const float*>(mine + kTailOffCv);
-        const int* ct = reinterpret_cast<const int*>(mine + kTailOffCt);
-        if (m.flags & ROW_CAND)
-          tail_exchange_row(p.peer, m, b, -INFINITY, -1, nsv, 0, [&](int i) { return Cand{cv[i], ct[i]}; }, mine, lane, p.tokens, p.scores);
-        else
-          tail_exchange_row(p.peer, m, b, ws, wt, 0, 0, [](int) { return Cand{0.f, 0}; }, mine, lane, p.tokens, p.scores);
-        r = 1;
-      }
-      if (lane == 0) p.row_flag[b] = r ? 0 : 1;
-      __syncwarp();
-    }
+    s_tail.a = a;
+    s_tail.peer = p.peer;
+    s_tail.row_flag = p.row_flag;
+    s_tail.B = p.B;
+    s_tail.mode = p.fuse_tail;
   }
+  __syncthreads();
+  int nw = min((int)(blockDim.x >> 5), kTailMaxWarps);
+  nw = min(nw, (int)(scratch_bytes / kTailWarpBytes));
+  lm_head_tail_rows(s_tail, scratch, nw);
   __syncthreads();
   dbg_stamp(p, 4);
   if (threadIdx.x == 0) *p.ticket = 0u;  // ready for the next launch on this handle

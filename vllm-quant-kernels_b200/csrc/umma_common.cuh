@@ -5,7 +5,6 @@
 
 #include "async_helpers.cuh"
 #include "lm_head.cuh"
-#include "tail.cuh"
 
 namespace vqk {
 namespace umma {
@@ -14,9 +13,8 @@ constexpr int BM = 128;        // vocab rows per tile = TMEM lanes
 constexpr int BK = 128;        // bytes of K per stage in shared memory: one 128-byte swizzle row
 constexpr int kMaxStages = 8;
 // sampler state of the four epilogue warps in shared memory: [4][3][BN] ints (slice maximum, best Gumbel
-// score, its token) and, for decode-sized batches, [4][kTailMaxBatch][kListLen] largest logits per column
-constexpr size_t kEpiListBytes = (size_t)4 * kTailMaxBatch * kListLen * sizeof(Cand);
-__host__ __device__ inline size_t epi_state_bytes(int bn) { return (size_t)12 * bn * sizeof(int) + kEpiListBytes; }
+// score, its token)
+__host__ __device__ inline size_t epi_state_bytes(int bn) { return (size_t)12 * bn * sizeof(int); }
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -133,8 +131,7 @@ __device__ __forceinline__ float key_to_float(int k) {
 template <int EPI, int BN, int NI = 1>
 __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, int lane, uint32_t tmem_base,
                                               uint64_t* tfull, uint64_t* tempty, volatile int* abort_flag,
-                                              const RowMeta* meta, int* sstate, const TileSched& sched, Cand* qlists,
-                                              uint64_t* qlists_free) {
+                                              const RowMeta* meta, int* sstate, const TileSched& sched) {
   constexpr bool INT8 = (EPI == 1);
   const int V = p.V, B = p.B;
     // ================================ epilogue =========================================
@@ -145,15 +142,6 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
     int* st_key = sstate + (size_t)(q * 3 + 1) * BN;   // best Gumbel score (ordered key)
     int* st_tok = sstate + (size_t)(q * 3 + 2) * BN;   // its local token id
     for (int b = lane; b < BN; b += 32) { st_max[b] = ordered_key(-INFINITY); st_key[b] = (int)0x80000000; st_tok[b] = 0x7fffffff; }
-    // decode-sized batches: the kListLen largest logits of every top-k column in this warp's rows
-    // (`qlists`: [4 warps][kTailMaxBatch][kListLen] entries of shared memory; when it is borrowed from a
-    // buffer the kernel's start-up still reads, `qlists_free` is the barrier that says it is done)
-    const bool use_lists = p.lists != nullptr && qlists != nullptr;
-    Cand* ql = qlists + (size_t)q * kTailMaxBatch * kListLen;
-    if (use_lists) {
-      if (qlists_free) mbar_wait_warp(qlists_free, 0, abort_flag);
-      for (int i = lane; i < kTailMaxBatch * kListLen; i += 32) ql[i] = Cand{-INFINITY, 0x7fffffff};
-    }
     __syncwarp();
     float xs_w8a8 = 1.f;
     if constexpr (INT8) xs_w8a8 = *reinterpret_cast<const float*>(p.xscale);
@@ -188,7 +176,7 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
         __half* cp = p.cand_logits + (long long)c0 * p.ld_cand + rowc;
         int mine_max = ordered_key(-INFINITY);
         tmem_ld_wait();
-        if (!p.bias && !post_ops && !use_lists && c0 + 16 <= B && (!p.do_sample || (candmask & 0xffffu) == 0xffffu)) {
+        if (!p.bias && !post_ops && c0 + 16 <= B && (!p.do_sample || (candmask & 0xffffu) == 0xffffu)) {
           // Fast path (all 16 columns exist and take the candidate path, or no sampling at all):
           // packed fp16 conversion, one store per column, and the 32-row maximum of every column
           // by a half2 butterfly over the warp instead of sixteen warp reductions.
@@ -265,22 +253,8 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
             if (lp && rok) lp[(long long)j * p.ld_logits] = h;
             if (candmask & (1u << j)) {
               if (rok) cp[(long long)j * p.ld_cand] = h;
-              if (use_lists) {
-                // lanes whose value beats the list's last entry hand it to lane 0, one after the other
-                const float l = __half2float(h);
-                Cand* e = ql + (c0 + j) * kListLen;
-                unsigned pass = __ballot_sync(0xffffffffu, rok && l > e[kListLen - 1].v);
-                while (pass) {
-                  const int src = __ffs(pass) - 1;
-                  pass &= pass - 1;
-                  const float v = __shfl_sync(0xffffffffu, l, src);
-                  if (lane == 0) list_insert(e, kListLen, v, tile_row0 + q * 32 + src);
-                  __syncwarp();
-                }
-              } else {
-                const int mk = __reduce_max_sync(0xffffffffu, rok ? ordered_key(__half2float(h)) : ordered_key(-INFINITY));
-                if (lane == j) mine_max = mk;
-              }
+              const int mk = __reduce_max_sync(0xffffffffu, rok ? ordered_key(__half2float(h)) : ordered_key(-INFINITY));
+              if (lane == j) mine_max = mk;
             } else if (livemask & (1u << j)) {
               const RowMeta m = meta[c0 + j];
               const float l = __half2float(h);
@@ -311,21 +285,10 @@ __device__ __forceinline__ void umma_epilogue(const LmHeadParams& p, int warp, i
       const int slice = blockIdx.x * 4 + q;
       for (int b = lane; b < B; b += 32) {
         const long long o = (long long)b * p.nslices + slice;
-        p.slice_max[o] = use_lists ? ql[b * kListLen].v : key_to_float(st_max[b]);
+        p.slice_max[o] = key_to_float(st_max[b]);
         p.part_score[o] = st_key[b] == (int)0x80000000 ? -INFINITY : key_to_float(st_key[b]);
         p.part_token[o] = st_tok[b];
       }
-      if (use_lists)
-        for (int b = lane; b < B; b += 32) {
-          SliceList rec;
-#pragma unroll
-          for (int i = 0; i < kListLen; ++i) {
-            rec.v[i] = __float2half_rn(ql[b * kListLen + i].v);
-            if (i < kListM) rec.t[i] = ql[b * kListLen + i].t;
-          }
-          rec.pad[0] = rec.pad[1] = rec.pad[2] = __float2half_rn(0.f);
-          p.lists[(long long)b * p.nslices + slice] = rec;
-        }
     }
 }
 
