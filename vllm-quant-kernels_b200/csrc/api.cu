@@ -272,7 +272,6 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const int sms = device_sm_count();
-  const int nslices = sms * 4;
   const int mode = h->mode;
   // Kernel choice: the register-streaming kernel for decode batches, the tcgen05 tensor-core
   // kernel once the batch is large enough that re-streaming the weights per 32 columns (or the
@@ -292,6 +291,8 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   if (use_umma) maxcols = umma_cols;
   else maxcols = stream_max_cols(mode, (int)h->H);
   if (maxcols <= 0) return VQK_ERR_UNSUPPORTED;
+  const int grid = sms;  // persistent kernels: one CTA per SM (144 CTAs, which fill the last round of 248320 rows, were no faster)
+  const int nslices = grid * 4;  // one slice per warp group (streaming kernel) or epilogue warp (tensor-core kernels)
 
   PeerTable pt{};
   if (peer) {
@@ -381,8 +382,8 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
         p.peer = pt;
       }
     }
-    rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, sms, st) : launch_lm_head_umma(mode, p, sms, st))
-                   : launch_lm_head_stream(mode, p, sms, st);
+    rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, grid, st) : launch_lm_head_umma(mode, p, grid, st))
+                   : launch_lm_head_stream(mode, p, grid, st);
     if (rc) return rc;
   }
   if (h->ev_stop) VQK_CUDA(cudaEventRecord(h->ev_stop, st));

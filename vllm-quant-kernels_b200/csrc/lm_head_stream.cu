@@ -1,17 +1,19 @@
 // Weight-streaming lm_head kernel for small batches (decode): one persistent CTA per SM,
-// 16 streaming warps = 4 groups x 4 warps, plus one epilogue warp per group.  A group owns one 16-row
+// 16 warps = 4 groups x 4 warps.  A group owns one 16-row
 // vocab tile at a time and its four warps split K; every lane streams 16 B (8 B / 4 B for the MX
 // modes) of two weight rows straight from HBM into registers in the layout of a warp-level MMA A
 // fragment, so the only per-byte ALU work is the int8 -> fp16 (or E2M1 -> e4m3) expansion.
 // Activations sit in shared memory, pre-arranged as B fragments.
-// The streaming warps never wait for one another: at the end of a tile each parks its split-K
+// The warps of a group do not run in lockstep: at the end of a tile each parks its split-K
 // partial sums in shared memory (two buffers per group, handed over through mbarriers) and goes
-// on with the next tile.  The group's epilogue warp adds the partials, applies the mode's scale,
-// rounds to fp16 exactly like the reference launchers, optionally stores the logits, and feeds
-// the sampler (per-slice lists of the largest logits, per-slice Gumbel winners) without a second
-// pass.  With the epilogue inside the streaming warps (two block barriers per tile) the W8A16
-// kernel ran 9 % slower.  Twenty warps leave 96 registers per thread, which is why a warp keeps ONE
-// set of weight registers and refills it unit by unit instead of double-buffering whole batches.
+// on with the next tile; the epilogue of a tile - add the partials, apply the mode's scale, round
+// to fp16 exactly like the reference launchers, optionally store the logits, feed the sampler
+// (per-slice lists of the largest logits, per-slice Gumbel winners) without a second pass - runs
+// one tile later, when every warp's partials have long arrived, the batch columns dealt out to
+// the four warps in rotation.  With the epilogue right behind its tile (two block barriers per
+// tile) the W8A16 kernel ran 9 % slower; epilogue warps of their own (20 warps, 96 registers)
+// could not keep up beyond four batch columns.  A warp keeps ONE set of weight registers and
+// refills it unit by unit instead of double-buffering whole batches.
 //
 // Replaces int8_gmv / int8_gemm / fp8_gemm / int8_w8a8_gemm / mxfp8_gemm / mxfp4_gemm of the
 // reference (src/vllm_quant_kernels/_kernels.py) for batch <= 32.
@@ -54,7 +56,7 @@ struct StreamBuf<MODE, U, true> {
 
 constexpr int kGroups = 4;
 constexpr int kStreamWarps = 4 * kGroups;
-constexpr int kThreads = (kStreamWarps + kGroups) * 32;  // warp 16 + g is group g's epilogue warp
+constexpr int kThreads = kStreamWarps * 32;
 
 // shared memory carve-up (bytes) -----------------------------------------------------------
 __host__ __device__ inline size_t stream_xfrag_bytes(int mode, int K, int NT) {
@@ -69,8 +71,54 @@ __host__ __device__ inline size_t stream_red_bytes(int NT) { return (size_t)2 * 
 // per warp group, batch column and tile row: running Gumbel (or greedy) winner of rows without top-k / top-p
 __host__ __device__ inline size_t stream_win_bytes(int NT) { return (size_t)kGroups * NT * 8 * 16 * sizeof(Cand); }
 constexpr size_t kStreamBarBytes = (size_t)(4 * kGroups + 1) * 8;  // full / free barriers of the partial-sum buffers, abort flag
-// per warp group and batch column: the kListLen largest logits of the group's slice (sampler, top-k rows)
-__host__ __device__ inline size_t stream_tlist_bytes(int NT) { return (size_t)kGroups * NT * 8 * kListLen * sizeof(Cand); }
+// Per warp group and batch column (sampler, top-k rows): the largest logits of the group's slice.
+// A logit above the column's threshold is APPENDED to a small buffer (every passing lane at once, no
+// order kept); when another pass might not fit, the buffer is cut back to its kListM largest and the
+// threshold raised to the next one.  The threshold is the witness: every logit of the slice that is
+// not in the buffer is <= it.  (A sorted list with one insertion per passing logit stalled its warp
+// for some 300 cycles a time, 35 times per column.)
+constexpr int kBufCap = 32;
+struct ColCtl {
+  int cnt;
+  float thr;
+};
+__host__ __device__ inline size_t stream_tlist_bytes(int NT) {
+  return (size_t)kGroups * NT * 8 * (kBufCap * sizeof(Cand) + sizeof(ColCtl));
+}
+__device__ __forceinline__ int stream_fkey(float f) {  // order-preserving float -> int (no NaN reaches it)
+  const int i = __float_as_int(f);
+  return i >= 0 ? i : (i ^ 0x7fffffff);
+}
+__device__ __forceinline__ float stream_fkey_inv(int k) { return __int_as_float(k >= 0 ? k : (k ^ 0x7fffffff)); }
+// whole warp: keep the kListM largest entries (sorted, ties: lower token first) in buf[0 .. kListM), the
+// rest of those slots at -inf; the threshold rises to the largest entry dropped
+__device__ __forceinline__ void col_compact(Cand* buf, ColCtl* ctl, int lane) {
+  const int n = ctl->cnt;  // warp-uniform, <= kBufCap
+  Cand e{-INFINITY, 0x7fffffff};
+  if (lane < n) e = buf[lane];
+  const int key = stream_fkey(e.v);
+  bool alive = lane < n;
+  int myrank = -1;
+  float dropped = -INFINITY;
+#pragma unroll
+  for (int r = 0; r <= kListM; ++r) {
+    const int mk = __reduce_max_sync(0xffffffffu, alive ? key : (int)0x80000000);
+    if (r < kListM) {
+      const int mt = __reduce_min_sync(0xffffffffu, (alive && key == mk) ? e.t : 0x7fffffff);
+      if (alive && key == mk && e.t == mt) { myrank = r; alive = false; }
+    } else if (n > kListM) {
+      dropped = stream_fkey_inv(mk);
+    }
+  }
+  __syncwarp();
+  if (myrank >= 0) buf[myrank] = e;
+  if (lane >= n && lane < kListM) buf[lane] = Cand{-INFINITY, 0x7fffffff};
+  if (lane == 0) {
+    ctl->cnt = n < kListM ? n : kListM;
+    if (n > kListM) ctl->thr = fmaxf(ctl->thr, dropped);
+  }
+  __syncwarp();
+}
 // (the sampler tail reuses the buffer once the main loop is over: one warp's scratch per batch row)
 __host__ __device__ inline size_t stream_smem_total(int mode, int K, int NT, int B) {
   const size_t main_loop = stream_xfrag_bytes(mode, K, NT) + stream_sx_bytes(mode, K, NT) + stream_red_bytes(NT) +
@@ -89,29 +137,29 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   float* sxf = reinterpret_cast<float*>(smem + stream_xfrag_bytes(MODE, p.K, NT));
   acc_t* red = reinterpret_cast<acc_t*>(smem + stream_xfrag_bytes(MODE, p.K, NT) + stream_sx_bytes(MODE, p.K, NT));
   RowMeta* meta = reinterpret_cast<RowMeta*>(reinterpret_cast<uint8_t*>(red) + stream_red_bytes(NT));
-  Cand* slist_all = reinterpret_cast<Cand*>(meta + NT * 8);                       // [group][column][entry]
-  Cand* swin = slist_all + (size_t)kGroups * NT * 8 * kListLen;                    // [group][column][tile row]
+  Cand* sbuf_all = reinterpret_cast<Cand*>(meta + NT * 8);                        // [group][column][kBufCap]
+  ColCtl* sctl_all = reinterpret_cast<ColCtl*>(sbuf_all + (size_t)kGroups * NT * 8 * kBufCap);  // [group][column]
+  Cand* swin = reinterpret_cast<Cand*>(sctl_all + kGroups * NT * 8);               // [group][column][tile row]
   uint64_t* fullb = reinterpret_cast<uint64_t*>(swin + (size_t)kGroups * NT * 8 * 16);  // [group][buffer]: partial sums parked
   uint64_t* freeb = fullb + 2 * kGroups;                                           // [group][buffer]: partial sums read
   volatile int* abort_flag = reinterpret_cast<volatile int*>(freeb + 2 * kGroups);
 
   dbg_stamp(p, 0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool is_epi = warp >= kStreamWarps;
-  const int group = (warp >> 2) & (kGroups - 1), wq = warp & 3;
+  const int group = warp >> 2, wq = warp & 3;
   const int g = lane >> 2, t = lane & 3;
   const int K = p.K, V = p.V, B = p.B;
   const int ngroups = K / GROUP;
   const int nks = (K + 63) / 64;
 
   if (p.do_sample) {
-    for (int i = tid; i < kGroups * NT * 8 * kListLen; i += kThreads) slist_all[i] = Cand{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < kGroups * NT * 8; i += kThreads) sctl_all[i] = ColCtl{0, -INFINITY};
     for (int i = tid; i < kGroups * NT * 8 * 16; i += kThreads) swin[i] = Cand{-INFINITY, 0x7fffffff};
   }
   if (tid == 0) {
     for (int i = 0; i < 2 * kGroups; ++i) {
       mbar_init(&fullb[i], 128);  // every thread of the group's four warps
-      mbar_init(&freeb[i], 32);   // every lane of the group's epilogue warp
+      mbar_init(&freeb[i], 128);
     }
     *abort_flag = 0;
   }
@@ -119,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   const int ntiles = (V + 15) / 16;
   const size_t rowbytes = (MODE == VQK_MODE_MXFP4) ? (size_t)K / 2 : (size_t)K;
   constexpr int kRedBuf = kStreamWarps * NT * 128;  // accumulators per buffer
-  acc_t* myred = red + (size_t)(warp & (kStreamWarps - 1)) * NT * 128;
+  acc_t* myred = red + (size_t)warp * NT * 128;
 
   // ---- main loop: a flat sequence of (tile, batch) steps per warp; a batch is U units.
   // EVEN (V % 16 == 0, every warp owns `per` whole units, per % U == 0) removes every bounds
@@ -266,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
 
   const int tstride = gridDim.x * kGroups;
   int tile = blockIdx.x * kGroups + group, bi = 0;
-  bool have = !is_epi && tile < ntiles;
+  bool have = tile < ntiles;
   if (have) {
     const BatchAddr a0 = locate(tile, 0);
 #pragma unroll
@@ -354,68 +402,36 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   __syncthreads();
 
 
-  // ---- streaming warps ------------------------------------------------------------------------
-  int tcount = 0;  // tiles this group has finished
-  while (have) {
-    int ntile = tile, nbi = bi + 1;
-    if (nbi == nb) { nbi = 0; ntile = tile + tstride; }
-    const bool nhave = ntile < ntiles;
-    // One set of registers, refilled unit by unit: as soon as a unit's MMAs have read it, the same
-    // registers fetch that unit of the NEXT batch (also across tile boundaries), so U units per lane
-    // are in flight all the time and the HBM stream of a warp never waits for its own arithmetic.
-    const BatchAddr nxt = locate(nhave ? ntile : tile, nhave ? nbi : bi);
-    const int u0 = ubeg + bi * U;
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      consume_unit(buf, u0, u);
-      if (nhave) load_unit(buf, nxt, u);
-      if constexpr (MX)
-        if ((u & 3) == 3 && nhave) load_scales(buf, nxt, u >> 2);
+  // ---- epilogue of the group's n-th tile (vocab rows etile * 16 ..), this warp's share of the columns:
+  // lane -> row (lane & 15) of the tile; column b is taken by warp (b + n) & 3, two columns per pass
+  // (one per half warp).  `rs`, `bias`: the row's scale and bias, fetched a tile ahead.
+  Cand* sbuf = sbuf_all + (size_t)group * NT * 8 * kBufCap;
+  ColCtl* sctl = sctl_all + group * NT * 8;
+  Cand* win = swin + (size_t)group * NT * 8 * 16;
+  const int er = lane & 15, eh = lane >> 4;
+  auto duty = [&](int n) { return (wq - n) & 3; };  // first column of this warp in tile n
+  auto fetch_row_scale = [&](int etile, float& rs, float& bias) {
+    const int row = etile * 16 + er;
+    rs = 1.f;
+    bias = 0.f;
+    if (row < V) {
+      if constexpr (MODE == VQK_MODE_W8A16 || MODE == VQK_MODE_FP8)
+        rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[row]);
+      if constexpr (MODE == VQK_MODE_W8A8) rs = reinterpret_cast<const float*>(p.wscale)[row];
+      if (p.bias) bias = __half2float(p.bias[row]);
     }
-    const bool tile_done = (bi == nb - 1);
-    tile = ntile; bi = nbi; have = nhave;
-    if (!tile_done) continue;
-
-    // ---- park the split-K partial sums for the epilogue warp and go on -----------------------
-    const int par = tcount & 1;
-    // (the buffer's previous contents, two tiles back, have been read: normally long ago)
-    if (!mbar_wait_warp(&freeb[group * 2 + par], (((uint32_t)tcount >> 1) & 1u) ^ 1u, abort_flag)) break;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      acc_t* r = myred + par * kRedBuf + nt * 128;
-      r[(2 * t) * 16 + g] = acc[nt][0];
-      r[(2 * t + 1) * 16 + g] = acc[nt][1];
-      r[(2 * t) * 16 + g + 8] = acc[nt][2];
-      r[(2 * t + 1) * 16 + g + 8] = acc[nt][3];
-      acc[nt][0] = 0; acc[nt][1] = 0; acc[nt][2] = 0; acc[nt][3] = 0;
-    }
-    mbar_arrive(&fullb[group * 2 + par]);
-    ++tcount;
-  }
-
-  // ---- epilogue warps: lane -> vocab row (lane & 15) of the tile, batch columns (lane >> 4) + 2j ----
-  if (is_epi) {
-    const int gi = warp - kStreamWarps;
-    const int er = lane & 15, eh = lane >> 4;
-    Cand* slist = slist_all + (size_t)gi * NT * 8 * kListLen;
-    Cand* win = swin + (size_t)gi * NT * 8 * 16;
-    int rnd = 0;
-    for (int etile = blockIdx.x * kGroups + gi; etile < ntiles; etile += tstride, ++rnd) {
+  };
+  auto epilogue = [&](int n, int etile, float rs, float bias) -> bool {
+    const int bfirst = duty(n);
+    const int par = n & 1;
+    if (bfirst < B) {
+      // every warp of the group has parked this tile's partial sums: a tile ago, as a rule
+      if (!mbar_wait_warp(&fullb[group * 2 + par], ((uint32_t)n >> 1) & 1u, abort_flag)) return false;
+      const acc_t* gred = red + par * kRedBuf + (size_t)(group * 4) * NT * 128;
       const int row = etile * 16 + er;
       const bool row_ok = row < V;
-      // the row's scale (and bias), in flight while the partial sums are awaited
-      float rs = 1.f, bias = 0.f;
-      if (row_ok) {
-        if constexpr (MODE == VQK_MODE_W8A16 || MODE == VQK_MODE_FP8)
-          rs = __half2float(reinterpret_cast<const __half*>(p.wscale)[row]);
-        if constexpr (MODE == VQK_MODE_W8A8) rs = reinterpret_cast<const float*>(p.wscale)[row];
-        if (p.bias) bias = __half2float(p.bias[row]);
-      }
-      const int par = rnd & 1;
-      if (!mbar_wait_warp(&fullb[gi * 2 + par], ((uint32_t)rnd >> 1) & 1u, abort_flag)) break;
-      const acc_t* gred = red + par * kRedBuf + (size_t)(gi * 4) * NT * 128;
-      for (int b0 = 0; b0 < B; b0 += 2) {  // two columns per pass, one per half warp
-        const int b = b0 + eh;
+      for (int bb = bfirst; bb < B; bb += 8) {
+        const int b = bb + 4 * eh;
         bool pass = false;  // a top-k column's logit that beats the last entry of the slice's list
         float l = 0.f;
         if (row_ok && b < B) {
@@ -434,34 +450,92 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
             l = __half2float(h);
             if (m.flags & ROW_CAND) {
               p.cand_logits[(long long)b * p.ld_cand + row] = h;
-              pass = l > slist[b * kListLen + kListM].v;
+              pass = l > sctl[b].thr;
             } else {
               float sc = l;
               if (!(m.flags & ROW_GREEDY)) {
                 sc = l / m.T + gumbel_noise(m.seed, (uint32_t)(row + p.sp.vocab_offset));
                 if ((m.flags & ROW_MASK_THR) && !(l >= m.thr)) sc = -INFINITY;
               }
-              const Cand w = win[b * 16 + er];  // this lane's own entry: local token id, offset added by the consumer
+              const Cand w = win[b * 16 + er];  // (row, column)'s own entry: local token id, offset added by the consumer
               if (better(sc, row, w.v, w.t)) win[b * 16 + er] = Cand{sc, row};
             }
           }
         }
         if (p.do_sample) {
-          // The slice's kListLen largest logits per column live in shared memory.  Once the list has
-          // warmed up hardly any logit beats its last entry, so this is one vote per tile; the few
-          // that do go in one after the other.
-          unsigned mask = __ballot_sync(0xffffffffu, pass);
-          while (mask) {
-            const int src = __ffs(mask) - 1;
-            mask &= mask - 1;
-            if (lane == src) list_insert(slist + b * kListLen, kListLen, l, row);
+          // logits above their column's threshold go into the column's buffer, all at once
+          const unsigned mask = __ballot_sync(0xffffffffu, pass);
+          if (mask) {
+            const unsigned hm = (mask >> (eh * 16)) & 0xffffu;  // this half warp's column
+            const bool colok = b < B;
+            int cnt = 0;
+            if (colok) cnt = sctl[b].cnt;  // <= kBufCap - 16 between passes
+            if (pass) sbuf[b * kBufCap + cnt + __popc(hm & ((1u << er) - 1u))] = Cand{l, row};
+            const int ncnt = cnt + __popc(hm);
             __syncwarp();
+            if (colok && er == 0 && hm) sctl[b].cnt = ncnt;
+            __syncwarp();
+            unsigned need = __ballot_sync(0xffffffffu, colok && er == 0 && ncnt > kBufCap - 16);
+            while (need) {  // cut a buffer back before another pass might not fit
+              const int src = __ffs(need) - 1;
+              need &= need - 1;
+              const int c = bb + 4 * (src >> 4);
+              col_compact(sbuf + c * kBufCap, sctl + c, lane);
+            }
           }
         }
       }
-      mbar_arrive(&freeb[gi * 2 + par]);
     }
+    mbar_arrive(&freeb[group * 2 + par]);  // this thread is done with the buffer (also when it had no column)
+    return true;
+  };
+
+  // ---- main loop ---------------------------------------------------------------------------------
+  int tcount = 0;       // tiles this group has finished
+  int ptile = 0;        // the previous one, whose epilogue is still due
+  float prs = 1.f, pbias = 0.f;
+  bool ok = true;
+  while (have) {
+    int ntile = tile, nbi = bi + 1;
+    if (nbi == nb) { nbi = 0; ntile = tile + tstride; }
+    const bool nhave = ntile < ntiles;
+    // One set of registers, refilled unit by unit: as soon as a unit's MMAs have read it, the same
+    // registers fetch that unit of the NEXT batch (also across tile boundaries), so U units per lane
+    // are in flight all the time and the HBM stream of a warp never waits for its own arithmetic.
+    const BatchAddr nxt = locate(nhave ? ntile : tile, nhave ? nbi : bi);
+    const int u0 = ubeg + bi * U;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      consume_unit(buf, u0, u);
+      if (nhave) load_unit(buf, nxt, u);
+      if constexpr (MX)
+        if ((u & 3) == 3 && nhave) load_scales(buf, nxt, u >> 2);
+    }
+    const bool tile_done = (bi == nb - 1);
+    const int this_tile = tile;
+    tile = ntile; bi = nbi; have = nhave;
+    if (!tile_done) continue;
+
+    // ---- the previous tile's epilogue, then park this tile's split-K partial sums and go on --------
+    if (tcount > 0 && !epilogue(tcount - 1, ptile, prs, pbias)) { ok = false; break; }
+    const int par = tcount & 1;
+    // (the buffer's previous contents, two tiles back, have been read by every warp)
+    if (!mbar_wait_warp(&freeb[group * 2 + par], (((uint32_t)tcount >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      acc_t* r = myred + par * kRedBuf + nt * 128;
+      r[(2 * t) * 16 + g] = acc[nt][0];
+      r[(2 * t + 1) * 16 + g] = acc[nt][1];
+      r[(2 * t) * 16 + g + 8] = acc[nt][2];
+      r[(2 * t + 1) * 16 + g + 8] = acc[nt][3];
+      acc[nt][0] = 0; acc[nt][1] = 0; acc[nt][2] = 0; acc[nt][3] = 0;
+    }
+    mbar_arrive(&fullb[group * 2 + par]);
+    ptile = this_tile;
+    if (duty(tcount) < B) fetch_row_scale(this_tile, prs, pbias);  // in flight until the epilogue, a tile from now
+    ++tcount;
   }
+  if (ok && tcount > 0) epilogue(tcount - 1, ptile, prs, pbias);
   __syncthreads();
 
   dbg_stamp(p, 1);
@@ -469,8 +543,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   if (p.do_sample) {
     if (warp < kGroups) {
       const int slice = blockIdx.x * kGroups + warp;
-      const Cand* slist = slist_all + (size_t)warp * NT * 8 * kListLen;
+      Cand* gbuf = sbuf_all + (size_t)warp * NT * 8 * kBufCap;
+      ColCtl* gctl = sctl_all + warp * NT * 8;
       const Cand* win = swin + (size_t)warp * NT * 8 * 16;
+      for (int b = 0; b < B; ++b) col_compact(gbuf + b * kBufCap, gctl + b, lane);  // kListM largest, sorted; threshold = witness
       for (int b0 = 0; b0 < B; b0 += 2) {
         const int b = b0 + (lane >> 4);
         Cand w{-INFINITY, 0x7fffffff};
@@ -486,15 +562,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
           if (p.lists) {
             SliceList rec;
 #pragma unroll
-            for (int i = 0; i < kListLen; ++i) {
-              const Cand c = slist[b * kListLen + i];
+            for (int i = 0; i < kListM; ++i) {
+              const Cand c = gbuf[b * kBufCap + i];
               rec.v[i] = __float2half_rn(c.v);
-              if (i < kListM) rec.t[i] = c.t;
+              rec.t[i] = c.t;
             }
+            rec.v[kListM] = __float2half_rn(gctl[b].thr);
             rec.pad[0] = rec.pad[1] = rec.pad[2] = __float2half_rn(0.f);
             p.lists[o] = rec;
           }
-          p.slice_max[o] = slist[b * kListLen].v;
+          p.slice_max[o] = gbuf[b * kBufCap].v;
           p.part_score[o] = w.v;
           p.part_token[o] = w.t;
         }
