@@ -75,7 +75,7 @@ struct LmHeadWs {
   float* slice_max;
   float* part_score;
   int* part_token;
-  SliceList* lists;  // decode-sized batches only
+  CtaList* lists;  // decode-sized batches only: [B][CTAs]
   int* row_flag;
   __half* cand;
   long long ld_cand;
@@ -135,7 +135,7 @@ static LmHeadWs carve_lm_head(void* base, int mode, long long V, long long K, lo
     w.slice_max = c.take<float>((size_t)B * nslices);
     w.part_score = c.take<float>((size_t)B * nslices);
     w.part_token = c.take<int>((size_t)B * nslices);
-    if (B <= kTailMaxBatch) w.lists = c.take<SliceList>((size_t)B * nslices);
+    if (B <= kTailMaxBatch) w.lists = c.take<CtaList>((size_t)B * (nslices / 4));
     w.row_flag = c.take<int>((size_t)B);
     w.ld_cand = (V + 7) & ~7LL;
     w.cand = c.take<__half>((size_t)B * w.ld_cand);

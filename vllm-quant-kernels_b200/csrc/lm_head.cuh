@@ -5,15 +5,20 @@
 
 namespace vqk {
 
-constexpr int kListM = 4;            // entries of a slice list that can be used ...
-constexpr int kListLen = kListM + 1;  // ... plus the witness: every logit of the slice outside the list is <= it
-// what an epilogue leaves per (row, slice) for the tail: two 16-byte words
-struct __align__(16) SliceList {
-  int t[kListM];       // local token ids of the kListM largest logits
-  __half v[kListLen];  // their values, descending, then the witness
-  __half pad[3];
+constexpr int kListM = 4;     // logits a warp group keeps per top-k column (its slice's largest), besides the witness
+constexpr int kCtaListM = 8;  // logits a CTA hands to the tail per top-k row: the largest of its groups' lists
+// What a CTA of the streaming kernel leaves per batch row for the sampler tail: four 16-byte words.
+// Every logit of the CTA's rows that is not among the kCtaListM listed ones is <= the witness.
+struct __align__(16) CtaList {
+  int t[kCtaListM];      // local token ids of the CTA's largest logits
+  __half v[kCtaListM];   // their values, descending (-inf: no entry)
+  __half witness;
+  __half pad;
+  float win_s;           // rows without top-k / top-p: the CTA's Gumbel (or greedy) winner
+  int win_t;             // its local token id
+  int pad2;
 };
-static_assert(sizeof(SliceList) == 32, "two 16-byte loads per slice");
+static_assert(sizeof(CtaList) == 64, "four 16-byte words per CTA and row");
 
 // Record exchange over peer memory (peer_exchange.cuh).  G == 0: no exchange.
 struct PeerTable {
@@ -49,7 +54,7 @@ struct LmHeadParams {
   unsigned long long* dbg;  // null, or [gridDim.x][16] time stamps (vqk_lm_head_set_debug_times)
   // decode-sized batches: the last CTA to finish resolves the rows (tail.cuh)
   int fuse_tail;
-  SliceList* lists;      // [B][nslices] largest logits per slice with LOCAL token ids (top-k rows); null: no lists
+  CtaList* lists;        // [B][gridDim.x] what every CTA hands to the tail (decode-sized batches); null: no tail
   unsigned int* ticket;  // device counter, zero between launches
   int* error;            // device error word, set when the tail's bounded wait for the grid runs out
   int* row_flag;         // [B] written by the tail: 1 = the row still needs the full-row kernel
@@ -78,7 +83,7 @@ __device__ __forceinline__ __half logit_post_ops(__half h, float soft_cap, float
 __device__ __forceinline__ void dbg_stamp(const LmHeadParams& p, int i) {
   if (p.dbg && threadIdx.x == 0) {
     unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t) :: "memory");
     p.dbg[(size_t)blockIdx.x * 16 + i] = t;
   }
 }

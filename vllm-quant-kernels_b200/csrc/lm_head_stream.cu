@@ -188,12 +188,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
     const uint8_t *pA, *pB, *sA, *sB;
     int u0;
   };
-  auto locate = [&](int tile, int bi) {
+  auto locate_at = [&](int tile, int u0) {
     const int row0 = tile * 16;
     const int rA = EVEN ? row0 + g : min(row0 + g, V - 1);
     const int rB = EVEN ? row0 + g + 8 : min(row0 + g + 8, V - 1);
     BatchAddr a;
-    a.u0 = ubeg + bi * U;
+    a.u0 = u0;
     a.pA = p.w + (size_t)rA * rowbytes + (size_t)a.u0 * UB + t * LB;
     a.pB = p.w + (size_t)rB * rowbytes + (size_t)a.u0 * UB + t * LB;
     a.sA = a.sB = nullptr;
@@ -204,6 +204,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
     }
     return a;
   };
+  auto locate = [&](int tile, int bi) { return locate_at(tile, ubeg + bi * U); };
   // unit u of a batch into its registers
   auto load_unit = [&](StreamBuf<MODE, U>& f, const BatchAddr& a, int u) {
     if constexpr (!MX) {
@@ -313,8 +314,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   };
 
   const int tstride = gridDim.x * kGroups;
+  // Whole tiles go round-robin over the grid's warp groups as long as every group gets one; the
+  // LEFTOVER tiles (fewer than groups) are taken one per CTA with K split over all sixteen warps, so the
+  // last round costs a quarter of a tile's time instead of a whole one at a fraction of the HBM rate
+  // (248320 rows on 148 CTAs: 26.2 rounds instead of 27; an eighth of those rows: 3.5 instead of 4).
+  const int units16 = units / 16;
+  const bool split_rest = !MX && EVEN && (units % 16) == 0 && units16 >= 1 && units16 <= U;
+  const int main_end = split_rest ? (ntiles / tstride) * tstride : ntiles;
+  const int rest_tile = main_end + (int)blockIdx.x;  // this CTA's first leftover tile
+  const bool rest_have = split_rest && rest_tile < ntiles;
+  bool rest_loaded = false;
   int tile = blockIdx.x * kGroups + group, bi = 0;
-  bool have = tile < ntiles;
+  bool have = tile < main_end;
   if (have) {
     const BatchAddr a0 = locate(tile, 0);
 #pragma unroll
@@ -405,9 +416,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   // ---- epilogue of the group's n-th tile (vocab rows etile * 16 ..), this warp's share of the columns:
   // lane -> row (lane & 15) of the tile; column b is taken by warp (b + n) & 3, two columns per pass
   // (one per half warp).  `rs`, `bias`: the row's scale and bias, fetched a tile ahead.
-  Cand* sbuf = sbuf_all + (size_t)group * NT * 8 * kBufCap;
-  ColCtl* sctl = sctl_all + group * NT * 8;
-  Cand* win = swin + (size_t)group * NT * 8 * 16;
   const int er = lane & 15, eh = lane >> 4;
   auto duty = [&](int n) { return (wq - n) & 3; };  // first column of this warp in tile n
   auto fetch_row_scale = [&](int etile, float& rs, float& bias) {
@@ -421,22 +429,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
       if (p.bias) bias = __half2float(p.bias[row]);
     }
   };
-  auto epilogue = [&](int n, int etile, float rs, float bias) -> bool {
-    const int bfirst = duty(n);
-    const int par = n & 1;
-    if (bfirst < B) {
-      // every warp of the group has parked this tile's partial sums: a tile ago, as a rule
-      if (!mbar_wait_warp(&fullb[group * 2 + par], ((uint32_t)n >> 1) & 1u, abort_flag)) return false;
-      const acc_t* gred = red + par * kRedBuf + (size_t)(group * 4) * NT * 128;
-      const int row = etile * 16 + er;
-      const bool row_ok = row < V;
-      for (int bb = bfirst; bb < B; bb += 8) {
-        const int b = bb + 4 * eh;
+  // the columns bfirst, bfirst + bstep, ... of one tile: `nparts` partial sums per logit, NT * 128 apart
+  // from gred; sampler state of warp group `sg`
+  auto epilogue_cols = [&](int etile, float rs, float bias, const acc_t* gred, int nparts, int bfirst, int bstep, int sg) {
+    Cand* sbuf = sbuf_all + (size_t)sg * NT * 8 * kBufCap;
+    ColCtl* sctl = sctl_all + sg * NT * 8;
+    Cand* win = swin + (size_t)sg * NT * 8 * 16;
+    const int row = etile * 16 + er;
+    const bool row_ok = row < V;
+      for (int bb = bfirst; bb < B; bb += 2 * bstep) {
+        const int b = bb + bstep * eh;
         bool pass = false;  // a top-k column's logit that beats the last entry of the slice's list
         float l = 0.f;
         if (row_ok && b < B) {
           const acc_t* q = gred + (b >> 3) * 128 + (b & 7) * 16 + er;
-          acc_t sum = q[0 * NT * 128] + q[1 * NT * 128] + q[2 * NT * 128] + q[3 * NT * 128];
+          acc_t sum = q[0];
+          for (int k = 1; k < nparts; ++k) sum += q[k * NT * 128];
           float v;
           if constexpr (MODE == VQK_MODE_W8A8) v = ((float)sum * rs) * xs_w8a8;   // _kernels.py:471, left to right
           else if constexpr (MX) v = sum;
@@ -479,12 +487,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
             while (need) {  // cut a buffer back before another pass might not fit
               const int src = __ffs(need) - 1;
               need &= need - 1;
-              const int c = bb + 4 * (src >> 4);
+              const int c = bb + bstep * (src >> 4);
               col_compact(sbuf + c * kBufCap, sctl + c, lane);
             }
           }
         }
-      }
+    }
+  };
+  // epilogue of the group's n-th whole tile: column b is taken by warp (b + n) & 3
+  auto epilogue = [&](int n, int etile, float rs, float bias) -> bool {
+    const int bfirst = duty(n);
+    const int par = n & 1;
+    if (bfirst < B) {
+      // every warp of the group has parked this tile's partial sums: a tile ago, as a rule
+      if (!mbar_wait_warp(&fullb[group * 2 + par], ((uint32_t)n >> 1) & 1u, abort_flag)) return false;
+      epilogue_cols(etile, rs, bias, red + par * kRedBuf + (size_t)(group * 4) * NT * 128, 4, bfirst, 4, group);
     }
     mbar_arrive(&freeb[group * 2 + par]);  // this thread is done with the buffer (also when it had no column)
     return true;
@@ -498,19 +515,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   while (have) {
     int ntile = tile, nbi = bi + 1;
     if (nbi == nb) { nbi = 0; ntile = tile + tstride; }
-    const bool nhave = ntile < ntiles;
+    const bool nhave = ntile < main_end;
     // One set of registers, refilled unit by unit: as soon as a unit's MMAs have read it, the same
     // registers fetch that unit of the NEXT batch (also across tile boundaries), so U units per lane
     // are in flight all the time and the HBM stream of a warp never waits for its own arithmetic.
-    const BatchAddr nxt = locate(nhave ? ntile : tile, nhave ? nbi : bi);
+    const bool nrest = !nhave && rest_have;  // the last whole batch: its registers go on to the leftover tile
+    const BatchAddr nxt = nrest ? locate_at(rest_tile, warp * units16) : locate(nhave ? ntile : tile, nhave ? nbi : bi);
     const int u0 = ubeg + bi * U;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       consume_unit(buf, u0, u);
-      if (nhave) load_unit(buf, nxt, u);
+      if (nhave || (nrest && u < units16)) load_unit(buf, nxt, u);
       if constexpr (MX)
         if ((u & 3) == 3 && nhave) load_scales(buf, nxt, u >> 2);
     }
+    rest_loaded = rest_loaded || nrest;
     const bool tile_done = (bi == nb - 1);
     const int this_tile = tile;
     tile = ntile; bi = nbi; have = nhave;
@@ -535,45 +554,102 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
     if (duty(tcount) < B) fetch_row_scale(this_tile, prs, pbias);  // in flight until the epilogue, a tile from now
     ++tcount;
   }
+  // ---- leftover tiles: one per CTA and sub-round, K split over the sixteen warps -------------------------
+  if (split_rest) {
+    for (int lt = rest_tile; lt < ntiles; lt += (int)gridDim.x) {  // CTA-uniform
+      const BatchAddr la = locate_at(lt, warp * units16);
+      if (!rest_loaded) {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (u < units16) load_unit(buf, la, u);
+      }
+      rest_loaded = false;
+      float lrs, lbias;
+      fetch_row_scale(lt, lrs, lbias);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (u < units16) consume_unit(buf, la.u0, u);
+      // the last whole tile's epilogue is still due (first sub-round); then both partial-sum buffers are free
+      if (ok && tcount > 0) ok = epilogue(tcount - 1, ptile, prs, pbias);
+      tcount = 0;
+      __syncthreads();
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        acc_t* r = myred + nt * 128;
+        r[(2 * t) * 16 + g] = acc[nt][0];
+        r[(2 * t + 1) * 16 + g] = acc[nt][1];
+        r[(2 * t) * 16 + g + 8] = acc[nt][2];
+        r[(2 * t + 1) * 16 + g + 8] = acc[nt][3];
+        acc[nt][0] = 0; acc[nt][1] = 0; acc[nt][2] = 0; acc[nt][3] = 0;
+      }
+      __syncthreads();
+      // column b by warp b & 15; the tile counts as part of the CTA's first slice
+      if (warp < B) epilogue_cols(lt, lrs, lbias, red, kStreamWarps, warp, kStreamWarps, 0);
+    }
+  }
   if (ok && tcount > 0) epilogue(tcount - 1, ptile, prs, pbias);
   __syncthreads();
 
   dbg_stamp(p, 1);
-  // ---- per-slice sampler results: warp w < 4 writes group w's, two columns per pass --------------
   if (p.do_sample) {
-    if (warp < kGroups) {
-      const int slice = blockIdx.x * kGroups + warp;
-      Cand* gbuf = sbuf_all + (size_t)warp * NT * 8 * kBufCap;
-      ColCtl* gctl = sctl_all + warp * NT * 8;
-      const Cand* win = swin + (size_t)warp * NT * 8 * 16;
-      for (int b = 0; b < B; ++b) col_compact(gbuf + b * kBufCap, gctl + b, lane);  // kListM largest, sorted; threshold = witness
-      for (int b0 = 0; b0 < B; b0 += 2) {
-        const int b = b0 + (lane >> 4);
-        Cand w{-INFINITY, 0x7fffffff};
-        if (b < B) w = win[b * 16 + (lane & 15)];
+    // ---- every warp cuts its share of its group's column buffers back to the kListM largest (sorted);
+    //      the threshold that remains is the group's witness
+    for (int b = wq; b < B; b += 4)
+      col_compact(sbuf_all + ((size_t)group * NT * 8 + b) * kBufCap, sctl_all + group * NT * 8 + b, lane);
+    __syncthreads();
+    // ---- per batch row (warp w takes rows w, w + 16): the per-slice results the full-row kernel reads,
+    //      and the CTA's record for the tail
+    for (int b = warp; b < B; b += kStreamWarps) {
+      Cand gw[2];  // winners of groups eh and 2 + eh (rows without top-k / top-p), complete in lanes 0 and 16
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        Cand w = swin[((size_t)(2 * h + eh) * NT * 8 + b) * 16 + er];
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
           const float s2 = __shfl_xor_sync(0xffffffffu, w.v, o);
           const int t2 = __shfl_xor_sync(0xffffffffu, w.t, o);
           if (better(s2, t2, w.v, w.t)) { w.v = s2; w.t = t2; }
         }
-        if (b < B && (lane & 15) == 0) {
-          const long long o = (long long)b * p.nslices + slice;
-          if (p.lists) {
-            SliceList rec;
-#pragma unroll
-            for (int i = 0; i < kListM; ++i) {
-              const Cand c = gbuf[b * kBufCap + i];
-              rec.v[i] = __float2half_rn(c.v);
-              rec.t[i] = c.t;
-            }
-            rec.v[kListM] = __float2half_rn(gctl[b].thr);
-            rec.pad[0] = rec.pad[1] = rec.pad[2] = __float2half_rn(0.f);
-            p.lists[o] = rec;
-          }
-          p.slice_max[o] = gbuf[b * kBufCap].v;
+        gw[h] = w;
+        if (er == 0) {
+          const long long o = (long long)b * p.nslices + blockIdx.x * kGroups + 2 * h + eh;
+          p.slice_max[o] = sbuf_all[((size_t)(2 * h + eh) * NT * 8 + b) * kBufCap].v;
           p.part_score[o] = w.v;
           p.part_token[o] = w.t;
+        }
+      }
+      if (p.lists) {
+        Cand cw = better(gw[1].v, gw[1].t, gw[0].v, gw[0].t) ? gw[1] : gw[0];
+        {
+          const float s2 = __shfl_xor_sync(0xffffffffu, cw.v, 16);
+          const int t2 = __shfl_xor_sync(0xffffffffu, cw.t, 16);
+          if (better(s2, t2, cw.v, cw.t)) { cw.v = s2; cw.t = t2; }
+        }
+        // the sixteen listed logits of the four groups (lane l < 16: group l / 4, entry l % 4), ranked
+        Cand c{-INFINITY, 0x7fffffff};
+        if (lane < 16) c = sbuf_all[((size_t)(lane >> 2) * NT * 8 + b) * kBufCap + (lane & 3)];
+        int rank = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float vj = __shfl_sync(0xffffffffu, c.v, j);
+          rank += (vj > c.v) || (vj == c.v && j < lane);
+        }
+        // witness: the groups' thresholds and the listed logits that do not fit the record
+        float wv = (lane < 16 && rank >= kCtaListM) ? c.v : -INFINITY;
+        if (lane >= 16 && lane < 16 + kGroups) wv = sctl_all[(lane - 16) * NT * 8 + b].thr;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) wv = fmaxf(wv, __shfl_xor_sync(0xffffffffu, wv, o));
+        CtaList* rec = p.lists + (size_t)b * gridDim.x + blockIdx.x;
+        if (lane < 16 && rank < kCtaListM) {
+          rec->t[rank] = c.t;
+          rec->v[rank] = __float2half_rn(c.v);
+        }
+        if (lane == 0) {
+          rec->witness = __float2half_rn(wv);
+          rec->pad = __float2half_rn(0.f);
+          rec->win_s = cw.v;
+          rec->win_t = cw.t;
+          rec->pad2 = 0;
         }
       }
     }

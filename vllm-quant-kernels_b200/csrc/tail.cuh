@@ -2,31 +2,29 @@
 // every CTA left in memory into the step's tokens, one warp per batch row, while those results are
 // still in L2.
 //
-// Per (row, slice) the epilogues leave
-//   * part_score / part_token   Gumbel (or greedy) winner of the slice, for rows without top-k / top-p;
-//   * slice_max and a list of the kListLen largest logits of the slice (the first kListM with
-//     their token ids), for rows with top-k.  The last list entry is the WITNESS: every logit of
-//     the slice that is not in the list is <= it.  Layout: list_v [row][position][slice],
-//     list_t [row][position][slice], so the tail reads runs of consecutive words.
-// A top-k row is resolved from the lists alone when they prove to hold every logit >= the k-th
-// largest of the row: t_k = k-th largest of the listed values, and every witness of a slice that
+// Per batch row every CTA leaves one 64-byte record (CtaList, lm_head.cuh):
+//   * the Gumbel (or greedy) winner of the CTA's vocab rows, for rows without top-k / top-p;
+//   * the kCtaListM largest logits of the CTA's vocab rows with their token ids, and a WITNESS: every
+//     logit of the CTA that is not listed is <= it, for rows with top-k.
+// A top-k row is resolved from the records alone when they prove to hold every logit >= the k-th
+// largest of the row: t_k = k-th largest of the listed values, and every witness of a CTA that
 // could matter is < t_k.  Then top-k (ties kept), top-p and the Gumbel argmax run on those few
 // values with the arithmetic of resolve_candidates in sampler.cu (same tokens, same scores).  A
-// row the lists cannot prove (more than kListM of the top k in one slice, top-p without top-k, a
-// threshold row with top-p, k > kTailMaxK) gets row_flag = 1 and is resolved from its fp16 logits
-// row by the full-row kernel (k_select), which is launched behind every step and returns at once
-// for rows whose flag is 0.
+// row the records cannot prove (more than kCtaListM of the top k in one CTA, or more than kListM in
+// one warp group's slice; top-p without top-k; a threshold row with top-p; k > kTailMaxK) gets
+// row_flag = 1 and is resolved from its fp16 logits row by the full-row kernel (k_select), which is
+// launched behind every step and returns at once for rows whose flag is 0.
 //
 // WHO runs it: the LAST CTA of the grid to finish (an atomic ticket; nobody waits for anybody).
 // HOW it is written: a single warp runs at the speed of its dependent latencies, not of its
-// instruction count - an L2 round trip costs it more than a microsecond, a shared-memory bisection
-// round some three hundred cycles.  (Measured on B200 with %globaltimer stamps: a version that
-// walked the data in small loops took 16 us per row, one with everything unrolled 21 us; running
-// either twice on the same SM did not make the second run faster, so it is not instruction fetch.)
-// So a row costs TWO dependent L2 trips - the slice maxima, four to a 16-byte load, then the
-// 32-byte list records of the few CTAs whose maximum can matter - and the selections run on
-// registers: the k-th largest of the 148 per-CTA maxima bounds the k-th largest logit from below
-// as the k-th largest slice maximum does, with a quarter of the keys.
+// instruction count - an L2 round trip costs it more than a microsecond, a selection round some
+// hundred cycles.  (Measured on B200 with %globaltimer stamps: a version that walked per-slice
+// data in small loops took 16 us per row, one with two dependent trips - slice maxima, then the
+// lists of the slices that can matter - 12 us.)  So a row costs ONE L2 trip: all the CTAs' records
+// (9.5 KB for 148 CTAs) come into shared memory with asynchronous 16-byte copies that need no
+// registers, and everything else runs on shared memory and registers: the k-th largest of the 148
+// per-CTA maxima bounds the k-th largest logit from below, the few listed values above that bound are
+// staged, and the k-th largest of those is t_k.
 //
 // All logits on this path are fp16 values, so their order is the order of 16-bit keys.
 #pragma once
@@ -36,30 +34,28 @@
 
 namespace vqk {
 
-constexpr int kTailMaxSlices = 1024;  // slices per row the tail can take (148 SMs x 4 = 592); a multiple of 4
-constexpr int kTailQuadRegs = kTailMaxSlices / 4 / 32;  // 16-byte loads of slice maxima per lane
-constexpr int kTailMaxK = 126;        // largest top-k resolved from the lists (a shard record holds as many)
-constexpr int kTailQuadCap = 128;     // CTAs (quads of slices) whose maximum can reach the k-th largest (k + ties)
-constexpr int kTailRecRegs = 8;       // list records per lane and round: 64 CTAs' worth
-constexpr int kTailStageCap = 1024;   // listed values >= tau0 a row may stage
+constexpr int kTailMaxCtas = 160;     // CTAs (records per row) the tail can take; 5 per lane
+constexpr int kTailCtaRegs = kTailMaxCtas / 32;
+constexpr int kTailMaxK = 126;        // largest top-k resolved from the records (a shard record holds as many)
+constexpr int kTailStageCap = 256;    // listed values >= the first bound a row may stage (k + ties + neighbours)
 constexpr int kTailSurvCap = 192;     // survivors of top-k (k + ties) resolved per row
 constexpr int kTailMaxWarps = 16;
 
-// Per-warp scratch (bytes).  Region A holds the head keys, slice ids and staged list entries while
-// a row is resolved from the lists, and afterwards the union of the shards' candidates (mv, mt);
-// region B holds the survivors and the top-p work arrays.
-constexpr int kTailOffQuads = 0;                                    // uint16 [kTailQuadCap]
-constexpr int kTailOffStage = kTailOffQuads + kTailQuadCap * 2;      // uint2  [kTailStageCap]: key, local token
+// Per-warp scratch (bytes).  Region A holds the CTAs' records while a row is resolved, and afterwards
+// the union of the shards' candidates (mv, mt); then the survivors and the top-p work arrays, which
+// the staged entries borrow until the survivors are known.
+constexpr int kTailOffRecs = 0;                                     // CtaList [kTailMaxCtas]
 constexpr int kTailOffMv = 0;                                       // float  [kMergeCap]
 constexpr int kTailOffMt = kTailOffMv + kMergeCap * 4;              // int    [kMergeCap]
-constexpr int kTailRegionA = ((kTailOffMt + kMergeCap * 4 > kTailOffStage + kTailStageCap * 8 ? kTailOffMt + kMergeCap * 4
-                                                                                              : kTailOffStage + kTailStageCap * 8) + 15) & ~15;
+constexpr int kTailRegionA = ((kTailOffMt + kMergeCap * 4 > kTailMaxCtas * 64 ? kTailOffMt + kMergeCap * 4 : kTailMaxCtas * 64) + 15) & ~15;
 constexpr int kTailOffCv = kTailRegionA;                            // float  [kTailSurvCap]
 constexpr int kTailOffCt = kTailOffCv + kTailSurvCap * 4;           // int    [kTailSurvCap]
 constexpr int kTailOffY = kTailOffCt + kTailSurvCap * 4;            // float  [kTailSurvCap]
 constexpr int kTailOffW = kTailOffY + kTailSurvCap * 4;             // uint64 [kTailSurvCap]
 constexpr int kTailOffAlive = kTailOffW + kTailSurvCap * 8;         // uint8  [kTailSurvCap]
+constexpr int kTailOffStage = kTailOffY;                            // uint2  [kTailStageCap]: key, local token
 constexpr int kTailWarpBytes = (kTailOffAlive + kTailSurvCap + 15) & ~15;
+static_assert(kTailStageCap * 8 <= kTailOffAlive - kTailOffY, "the staged entries fit the top-p work arrays");
 static_assert(kTailOffW % 8 == 0, "mass array alignment");
 
 // shared memory the tail wants from a CTA for `rows` batch rows (it makes do with less: fewer rows at a time)
@@ -331,8 +327,9 @@ struct TailArgs {
   const float* slice_max;
   const float* part_score;
   const int* part_token;
-  const SliceList* lists;
+  const CtaList* lists;  // [rows][ncta]
   int nslices;
+  int ncta;
   long long* tokens;
   float* scores;
   uint8_t* records;
@@ -355,11 +352,13 @@ struct TailRowResult {
 static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a, const RowMeta& m, int b, uint8_t* scratch,
                                                               int lane, bool exchange) {
   TailRowResult res{0, 0, -INFINITY, 0x7fffffff};
-  const int nsl = a.nslices;
   const long long voff = a.sp.vocab_offset;
   const unsigned lt = (1u << lane) - 1u;
-  if (!(m.flags & ROW_CAND)) {
-    // per-slice winners -> row winner (the same merge k_select does for these rows)
+  const int ncta = a.ncta;
+  if (!a.lists || ncta > kTailMaxCtas) {
+    if (m.flags & ROW_CAND) return res;
+    // no records (a kernel without them): per-slice winners -> row winner, as k_select merges them
+    const int nsl = a.nslices;
     float s = -INFINITY;
     int t = 0x7fffffff;
 #pragma unroll 4
@@ -380,98 +379,96 @@ static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a,
     }
     return res;
   }
-  if (!a.lists || m.top_k <= 0 || m.top_k > kTailMaxK || nsl > kTailMaxSlices || (nsl & 3)) return res;
+  // 1. the one trip: every CTA's record of this row into shared memory (L2 -> shared, no registers held)
+  CtaList* recs = reinterpret_cast<CtaList*>(scratch + kTailOffRecs);
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(a.lists + (long long)b * ncta);
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(recs);
+    for (int i = lane; i < ncta * 4; i += 32)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)i * 16u), "l"(src + i) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+  }
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); a.dbg[5] = t_; }
+  if (!(m.flags & ROW_CAND)) {
+    // the CTAs' winners -> row winner (the same merge k_select does for these rows)
+    float s = -INFINITY;
+    int t = 0x7fffffff;
+    for (int c = lane; c < ncta; c += 32)
+      if (better(recs[c].win_s, recs[c].win_t, s, t)) { s = recs[c].win_s; t = recs[c].win_t; }
+    warp_best_pair(s, t);
+    const long long tok = (long long)t + voff;
+    res.win_s = s;
+    res.win_t = (int)tok;
+    res.status = exchange ? 2 : 1;
+    if (!exchange && lane == 0) {
+      tail_write_header(a.records, b, s, (int)tok, 0, 0);
+      if (a.tokens) a.tokens[b] = tok;
+      if (a.scores) a.scores[b] = s;
+    }
+    return res;
+  }
+  if (m.top_k <= 0 || m.top_k > kTailMaxK) return res;
 
-  uint16_t* qsel = reinterpret_cast<uint16_t*>(scratch + kTailOffQuads);
   uint2* st = reinterpret_cast<uint2*>(scratch + kTailOffStage);
   float* cv = reinterpret_cast<float*>(scratch + kTailOffCv);
   int* ct = reinterpret_cast<int*>(scratch + kTailOffCt);
   const int K = m.top_k;
-  const int nq = nsl >> 2;  // CTAs: four consecutive slices each
-  const float4* heads4 = reinterpret_cast<const float4*>(a.slice_max + (long long)b * nsl);
-  const uint4* recs = reinterpret_cast<const uint4*>(a.lists + (long long)b * nsl);
-
-  // 1. trip one: the slice maxima, one 16-byte load per CTA; key of a CTA = its largest
-  uint32_t qk[kTailQuadRegs];
+  // 2. key of a CTA = its largest logit; tau0 = K-th largest of those: K distinct logits are >= it,
+  //    so the K-th largest logit of the row is too
+  uint32_t qk[kTailCtaRegs];
   int nfin = 0;
 #pragma unroll
-  for (int j = 0; j < kTailQuadRegs; ++j) {
-    float4 h = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    if (j * 32 + lane < nq) h = __ldcg(heads4 + j * 32 + lane);
-    qk[j] = h16_key(fmaxf(fmaxf(h.x, h.y), fmaxf(h.z, h.w)));
+  for (int j = 0; j < kTailCtaRegs; ++j) {
+    const int c = j * 32 + lane;
+    qk[j] = c < ncta ? h16_bits_key(__half_as_ushort(recs[c].v[0])) : 0u;
     nfin += (qk[j] >= kKeyLowestFinite);
   }
   nfin = __reduce_add_sync(0xffffffffu, nfin);
-  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[5] = t_; }
-  // 2. tau0 = K-th largest CTA maximum: K distinct logits are >= it, so the K-th largest logit is
-  //    (bisection on the 16 key bits; every round is kTailQuadRegs compares and one warp vote)
   uint32_t tau0 = kKeyLowestFinite;
   if (nfin >= K) tau0 = warp_kth_largest_reg(qk, K);
   if (tau0 < kKeyLowestFinite) tau0 = kKeyLowestFinite;
-  // 3. the CTAs that can hold a logit >= tau0
-  int nsel = 0;
-#pragma unroll
-  for (int j = 0; j < kTailQuadRegs; ++j) {
-    const bool hit = qk[j] >= tau0;  // unused slots hold key(-inf)
-    const unsigned mask = __ballot_sync(0xffffffffu, hit);
-    const int pos = nsel + __popc(mask & lt);
-    if (hit && pos < kTailQuadCap) qsel[pos] = (uint16_t)(j * 32 + lane);
-    nsel += __popc(mask);
-  }
-  if (nsel > kTailQuadCap) return res;
-  __syncwarp();
-  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[6] = t_; }
-  // 4. trip two: the list records of their slices (two 16-byte loads each, up to kTailRecRegs per lane
-  //    in flight at once); every listed value >= tau0 is staged as (key, token); witnesses are folded
-  //    to a maximum
-  const int nrec = nsel * 4;
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); a.dbg[6] = t_; }
+  // 3. every listed value >= tau0 is staged as (key, token); the witnesses of the CTAs that reach tau0
+  //    are folded to a maximum (a CTA whose largest logit is below tau0 hides nothing that matters)
   uint32_t wkey = 0;
-  int ne = 0;
-#pragma unroll 1
-  for (int base = 0; base < nrec; base += kTailRecRegs * 32) {
-    uint4 rt[kTailRecRegs], rv[kTailRecRegs];
+  int mine_n = 0;
+  uint32_t cnts = 0;  // per CTA of this lane: how many of its listed values reach tau0 (4 bits each)
 #pragma unroll
-    for (int r = 0; r < kTailRecRegs; ++r) {
-      const int i = base + r * 32 + lane;
-      rt[r] = make_uint4(0, 0, 0, 0);
-      rv[r] = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0);  // five times -inf
-      if (i < nrec) {
-        const int slice = (int)qsel[i >> 2] * 4 + (i & 3);
-        rt[r] = __ldcg(recs + 2 * slice);
-        rv[r] = __ldcg(recs + 2 * slice + 1);
-      }
-    }
-    int mine_n = 0;
+  for (int j = 0; j < kTailCtaRegs; ++j) {
+    if (qk[j] >= tau0) {  // (unused slots hold key 0)
+      const int c = j * 32 + lane;
+      const uint4 hv = *reinterpret_cast<const uint4*>(recs[c].v);
+      const uint32_t w[4] = {hv.x, hv.y, hv.z, hv.w};
+      int n = 0;
 #pragma unroll
-    for (int r = 0; r < kTailRecRegs; ++r) {
-      const uint32_t k0 = h16_bits_key(rv[r].x), k1 = h16_bits_key(rv[r].x >> 16);
-      const uint32_t k2 = h16_bits_key(rv[r].y), k3 = h16_bits_key(rv[r].y >> 16);
-      const uint32_t kw = h16_bits_key(rv[r].z);
-      if (k0 >= tau0) wkey = max(wkey, kw);  // a slice whose maximum is below tau0 hides nothing that matters
-      mine_n += (k0 >= tau0) + (k1 >= tau0) + (k2 >= tau0) + (k3 >= tau0);
-      rv[r] = make_uint4(k0, k1, k2, k3);    // keep the keys
+      for (int i = 0; i < kCtaListM; ++i) n += (h16_bits_key(w[i >> 1] >> (16 * (i & 1))) >= tau0);  // descending: a prefix
+      cnts |= (uint32_t)n << (4 * j);
+      mine_n += n;
+      wkey = max(wkey, h16_bits_key(__half_as_ushort(recs[c].witness)));
     }
-    int incl = mine_n;  // prefix over the lanes: where this lane's staged entries go
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int t2 = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t2;
-    }
-    const int batch = __shfl_sync(0xffffffffu, incl, 31);
-    if (ne + batch > kTailStageCap) return res;
-    int wpos = ne + incl - mine_n;
-#pragma unroll
-    for (int r = 0; r < kTailRecRegs; ++r) {
-      if (rv[r].x >= tau0) st[wpos++] = make_uint2(rv[r].x, rt[r].x);
-      if (rv[r].y >= tau0) st[wpos++] = make_uint2(rv[r].y, rt[r].y);
-      if (rv[r].z >= tau0) st[wpos++] = make_uint2(rv[r].z, rt[r].z);
-      if (rv[r].w >= tau0) st[wpos++] = make_uint2(rv[r].w, rt[r].w);
-    }
-    ne += batch;
   }
+  int incl = mine_n;  // prefix over the lanes: where this lane's staged entries go
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t2 = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t2;
+  }
+  const int ne = __shfl_sync(0xffffffffu, incl, 31);
   wkey = __reduce_max_sync(0xffffffffu, wkey);
+  if (ne > kTailStageCap) return res;
+  {
+    int wpos = incl - mine_n;
+#pragma unroll
+    for (int j = 0; j < kTailCtaRegs; ++j) {
+      const int n = (int)((cnts >> (4 * j)) & 15u);
+      const int c = j * 32 + lane;
+      for (int i = 0; i < n; ++i) st[wpos++] = make_uint2(h16_bits_key(__half_as_ushort(recs[c].v[i])), (uint32_t)recs[c].t[i]);
+    }
+  }
   __syncwarp();
-  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[7] = t_; }
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); a.dbg[7] = t_; }
   // 5. t_k: the K-th largest staged value (every staged value survives when fewer than K exist)
   uint32_t tk = kKeyLowestFinite;
   if (ne >= K) {
@@ -479,15 +476,17 @@ static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a,
       uint32_t sk[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) sk[j] = j * 32 + lane < ne ? st[j * 32 + lane].x : 0u;
-      const uint32_t prefix = warp_kth_largest_reg(sk, K);
-      tk = prefix;
+      tk = warp_kth_largest_reg(sk, K);
     } else {
-      tk = warp_kth_largest_key([&](int i) { return st[i].x; }, ne, K, 15, 0, lane);
+      uint32_t sk[kTailStageCap / 32];
+#pragma unroll
+      for (int j = 0; j < kTailStageCap / 32; ++j) sk[j] = j * 32 + lane < ne ? st[j * 32 + lane].x : 0u;
+      tk = warp_kth_largest_reg(sk, K);
     }
   }
-  // 6. the proof: no slice we looked at hides a value >= t_k (the others have maximum < tau0 <= t_k)
+  // 6. the proof: no CTA we looked at hides a value >= t_k (the others have maximum < tau0 <= t_k)
   if (wkey >= tk) return res;
-  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[10] = t_; }
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); a.dbg[10] = t_; }
   // 7. survivors (>= t_k, ties kept), with their GLOBAL token ids
   int nsv = 0;
 #pragma unroll 1
@@ -518,7 +517,7 @@ static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a,
   }
   res.status = 1;
   if (!a.single_shard) return res;
-  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.dbg[11] = t_; }
+  if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); a.dbg[11] = t_; }
   // 8. top-p over the survivors, then the Gumbel argmax
   const TailWinner w = nsv <= 64 ? warp_topp_gumbel64(cv, ct, nsv, m.T, m.top_p, m.seed, lane)
                                  : warp_topp_gumbel(cv, ct, nsv, m.T, m.top_p, m.seed,
@@ -592,7 +591,7 @@ __device__ __forceinline__ void lm_head_tail(const LmHeadParams& p, const RowMet
   if (threadIdx.x == 0) {
     TailArgs a;
     a.sp = p.sp; a.slice_max = p.slice_max; a.part_score = p.part_score; a.part_token = p.part_token;
-    a.lists = p.lists; a.nslices = p.nslices; a.tokens = p.tokens; a.scores = p.scores;
+    a.lists = p.lists; a.nslices = p.nslices; a.ncta = (int)gridDim.x; a.tokens = p.tokens; a.scores = p.scores;
     a.records = p.records; a.single_shard = p.single_shard;
     a.dbg = p.dbg ? p.dbg + (size_t)blockIdx.x * 16 : nullptr;
     s_tail.a = a;
