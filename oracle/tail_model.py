@@ -12,6 +12,12 @@ row from those alone when they PROVE to contain every logit >= the k-th largest 
   t_k = k-th largest candidate
   proof: every witness of those slices is < t_k   (slices that were skipped have maximum < tau0 <= t_k)
 
+The streaming kernel applies the argument at two levels: every warp group keeps such a list for
+its slice (M = 4), and at its end every CTA merges the lists of its four groups into ONE record per
+row (``cta_records``: the 8 largest listed values with their tokens, and a witness that bounds
+every logit of the CTA that is not in the record); the tail then runs the argument above with
+"slice" = CTA and M = 8.
+
 This module computes the same thing with sorts, so a test can check (a) that whenever the proof
 holds the candidate set >= t_k IS the exact top-k set with ties, and (b) that the proof fails
 where it must (more than M of the top k in one slice).
@@ -64,3 +70,26 @@ def resolve_from_lists(vals: np.ndarray, toks: np.ndarray, k: int):
     proved = bool(witness < t_k) or (not np.isfinite(witness) and not np.isfinite(t_k))
     surv = cand_v >= t_k
     return proved, cand_t[surv], cand_v[surv]
+
+
+def cta_records(vals: np.ndarray, toks: np.ndarray, groups: int = 4, M2: int = 8):
+    """Merge of the warp groups' lists (slices ``c * groups .. c * groups + groups - 1`` belong to CTA
+    c) into per-CTA records, as the streaming kernel's last step does: the M2 largest listed values
+    of the CTA with their tokens, and the witness = max(the groups' witnesses, the listed values that
+    did not fit).  Same shapes as ``slice_lists`` returns, so ``resolve_from_lists`` takes them."""
+    nsl, M = toks.shape
+    ncta = nsl // groups
+    out_v = np.full((ncta, M2 + 1), -np.inf, dtype=F32)
+    out_t = np.full((ncta, M2), -1, dtype=np.int64)
+    for c in range(ncta):
+        v = vals[c * groups:(c + 1) * groups, :M].ravel()
+        t = toks[c * groups:(c + 1) * groups].ravel()
+        order = np.lexsort((np.arange(v.size), -v.astype(np.float64)))
+        keep, rest = order[:M2], order[M2:]
+        out_v[c, :keep.size] = v[keep]
+        out_t[c, :keep.size] = t[keep]
+        w = vals[c * groups:(c + 1) * groups, M].max()
+        if rest.size:
+            w = max(w, v[rest].max())
+        out_v[c, M2] = w
+    return out_v, out_t

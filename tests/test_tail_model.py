@@ -59,3 +59,31 @@ def test_ties_at_the_threshold_are_kept_or_refused_never_dropped():
     vals, toks = TM.slice_lists(short, slices, nsl)
     ok, _, _ = TM.resolve_from_lists(vals, toks, 50)
     assert not ok
+
+
+def test_cta_records_bound_what_they_leave_out_and_decide_like_the_slice_lists():
+    V, nsl = 248320, 592
+    slices = TM.slice_of_rows(V, nsl)
+    ctas = slices // 4
+    for seed in range(6):
+        row = OS.synth_logits(1, V, seed=100 + seed)[0].astype(np.float16).astype(np.float32)
+        vals, toks = TM.slice_lists(row, slices, nsl)
+        cv, ct = TM.cta_records(vals, toks)
+        for c in (0, 17, 147):                              # the witness bounds every logit the record leaves out
+            mine = np.nonzero(ctas == c)[0]
+            listed = set(ct[c][ct[c] >= 0].tolist())
+            left = np.array([i for i in mine.tolist() if i not in listed])
+            assert row[left].max() <= cv[c, 8]
+            assert (np.diff(cv[c, :8]) <= 0).all()
+        for k in (1, 50, 126):
+            ok, t, v = TM.resolve_from_lists(cv, ct, k)
+            if ok:
+                assert set(t.tolist()) == _exact_topk(row, k), (seed, k)
+    # five of the top ten in one warp group: its list holds four, the CTA's witness must refuse the row
+    rng = np.random.default_rng(1)
+    row = rng.standard_normal(16 * 592 * 4).astype(np.float32)
+    sl = TM.slice_of_rows(row.size, nsl)
+    row[np.nonzero(sl == 9)[0][:5]] = 30.0 + np.arange(5)
+    vals, toks = TM.slice_lists(row, sl, nsl)
+    ok, _, _ = TM.resolve_from_lists(*TM.cta_records(vals, toks), 10)
+    assert not ok

@@ -85,25 +85,37 @@ constexpr uint32_t kKeyLowestFinite = 0x0400u;  // key(-65504); key(-inf) = 0x03
 // below every candidate >= kKeyLowestFinite that can win), three key bits per round: each round
 // counts the keys >= seven thresholds at once (the counts packed ten bits apiece into three words,
 // so a round costs three warp reductions instead of one per bit).  At least k keys must be
-// >= kKeyLowestFinite.  Result in every lane.
+// >= kKeyLowestFinite.  The bits all those keys share (they usually agree in sign and exponent) are
+// found with two reductions first and cost no round.  Result in every lane.
 template <int R>
 __device__ __forceinline__ uint32_t warp_kth_largest_reg(const uint32_t (&key)[R], int k) {
   static_assert(R * 32 < 1024, "a count must fit ten bits");
-  uint32_t prefix = 0;
+  uint32_t hi = 0, lo = 0xffffu;
+#pragma unroll
+  for (int j = 0; j < R; ++j) {
+    hi = max(hi, key[j]);
+    if (key[j] >= kKeyLowestFinite) lo = min(lo, key[j]);
+  }
+  hi = __reduce_max_sync(0xffffffffu, hi);
+  lo = __reduce_min_sync(0xffffffffu, lo);
+  int nbits = 32 - __clz((hi ^ lo) | 0u);  // low bits in which the keys differ (0: all equal)
+  if (hi == lo) return hi;
+  uint32_t prefix = hi & ~((1u << nbits) - 1u);
 #pragma unroll 1
-  for (int shift = 13; shift >= -2; shift -= 3) {
-    // thresholds prefix | t << shift, t = 1..7 (the last round, shift = -2, has one bit left: t = 1 only)
-    const int sh = shift < 0 ? 0 : shift;
-    const int nt = shift < 0 ? 1 : 7;
+  while (nbits > 0) {
+    // thresholds prefix | t << sh, t = 1 .. nt
+    const int w = nbits >= 3 ? 3 : nbits;
+    const int sh = nbits - w;
+    const int nt = (1 << w) - 1;
     uint32_t c0 = 0, c1 = 0, c2 = 0;  // counts of t = 1..3 | 4..6 | 7
 #pragma unroll
     for (int j = 0; j < R; ++j) {
       const uint32_t kj = key[j];
       c0 += (kj >= (prefix | (1u << sh))) + ((uint32_t)(nt > 1 && kj >= (prefix | (2u << sh))) << 10) +
-            ((uint32_t)(nt > 1 && kj >= (prefix | (3u << sh))) << 20);
-      c1 += (uint32_t)(nt > 1 && kj >= (prefix | (4u << sh))) + ((uint32_t)(nt > 1 && kj >= (prefix | (5u << sh))) << 10) +
-            ((uint32_t)(nt > 1 && kj >= (prefix | (6u << sh))) << 20);
-      c2 += (uint32_t)(nt > 1 && kj >= (prefix | (7u << sh)));
+            ((uint32_t)(nt > 2 && kj >= (prefix | (3u << sh))) << 20);
+      c1 += (uint32_t)(nt > 3 && kj >= (prefix | (4u << sh))) + ((uint32_t)(nt > 3 && kj >= (prefix | (5u << sh))) << 10) +
+            ((uint32_t)(nt > 3 && kj >= (prefix | (6u << sh))) << 20);
+      c2 += (uint32_t)(nt > 3 && kj >= (prefix | (7u << sh)));
     }
     c0 = __reduce_add_sync(0xffffffffu, c0);
     c1 = __reduce_add_sync(0xffffffffu, c1);
@@ -118,6 +130,7 @@ __device__ __forceinline__ uint32_t warp_kth_largest_reg(const uint32_t (&key)[R
     if ((int)(c1 >> 20) >= k) t = 6;
     if ((int)c2 >= k) t = 7;
     prefix |= t << sh;
+    nbits = sh;
   }
   return prefix;
 }
@@ -214,7 +227,7 @@ static __device__ __noinline__ TailWinner warp_topp_gumbel(const float* cv, cons
     unsigned long long z = 0;
 #pragma unroll 1
     for (int i = lane; i < n; i += 32) {
-      const unsigned long long wi = (unsigned long long)((double)expf(y[i] - mx) * 1099511627776.0);
+      const unsigned long long wi = __float2ull_rz(expf(y[i] - mx) * 1099511627776.0f);  // exact scaling: the value mass_of (sampler.cu) computes in double
       w[i] = wi;
       z += wi;
     }
@@ -257,8 +270,8 @@ static __device__ __noinline__ TailWinner warp_topp_gumbel64(const float* cv, co
     float mx = fmaxf(y0, y1);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    const unsigned long long w0 = h0 ? (unsigned long long)((double)expf(y0 - mx) * 1099511627776.0) : 0ull;
-    const unsigned long long w1 = h1 ? (unsigned long long)((double)expf(y1 - mx) * 1099511627776.0) : 0ull;
+    const unsigned long long w0 = h0 ? __float2ull_rz(expf(y0 - mx) * 1099511627776.0f) : 0ull;  // = mass_of (sampler.cu): the scaling is exact
+    const unsigned long long w1 = h1 ? __float2ull_rz(expf(y1 - mx) * 1099511627776.0f) : 0ull;
     unsigned long long z = w0 + w1;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
@@ -430,43 +443,41 @@ static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a,
   if (nfin >= K) tau0 = warp_kth_largest_reg(qk, K);
   if (tau0 < kKeyLowestFinite) tau0 = kKeyLowestFinite;
   if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); a.dbg[6] = t_; }
-  // 3. every listed value >= tau0 is staged as (key, token); the witnesses of the CTAs that reach tau0
-  //    are folded to a maximum (a CTA whose largest logit is below tau0 hides nothing that matters)
-  uint32_t wkey = 0;
-  int mine_n = 0;
-  uint32_t cnts = 0;  // per CTA of this lane: how many of its listed values reach tau0 (4 bits each)
-#pragma unroll
+  // 3. every listed value >= tau0 is staged as (fp16 bits, token), in no particular order (a position
+  //    counter in shared memory); the witnesses of the CTAs that reach tau0 are folded to a maximum (a
+  //    CTA whose largest logit is below tau0 hides nothing that matters)
+  int* stage_n = reinterpret_cast<int*>(scratch + kTailOffAlive);
+  if (lane == 0) *stage_n = 0;
+  __syncwarp();
+  const float tau0f = h16_key_to_float(tau0);
+  float wmax = -INFINITY;
+  bool spill = false;
+#pragma unroll 1
   for (int j = 0; j < kTailCtaRegs; ++j) {
-    if (qk[j] >= tau0) {  // (unused slots hold key 0)
-      const int c = j * 32 + lane;
+    const int c = j * 32 + lane;
+    if (c < ncta && __half2float(recs[c].v[0]) >= tau0f) {
       const uint4 hv = *reinterpret_cast<const uint4*>(recs[c].v);
-      const uint32_t w[4] = {hv.x, hv.y, hv.z, hv.w};
-      int n = 0;
+      const __half2* h2 = reinterpret_cast<const __half2*>(&hv);
+      int n = 0;  // descending values: those >= tau0 are a prefix
 #pragma unroll
-      for (int i = 0; i < kCtaListM; ++i) n += (h16_bits_key(w[i >> 1] >> (16 * (i & 1))) >= tau0);  // descending: a prefix
-      cnts |= (uint32_t)n << (4 * j);
-      mine_n += n;
-      wkey = max(wkey, h16_bits_key(__half_as_ushort(recs[c].witness)));
+      for (int i = 0; i < kCtaListM / 2; ++i) {
+        const float2 f = __half22float2(h2[i]);
+        n += (f.x >= tau0f) + (f.y >= tau0f);
+      }
+      wmax = fmaxf(wmax, __half2float(recs[c].witness));
+      const int pos = atomicAdd(stage_n, n);
+      if (pos + n <= kTailStageCap) {
+        const unsigned short* hb = reinterpret_cast<const unsigned short*>(recs[c].v);
+        for (int i = 0; i < n; ++i) st[pos + i] = make_uint2((uint32_t)hb[i], (uint32_t)recs[c].t[i]);
+      } else {
+        spill = true;
+      }
     }
   }
-  int incl = mine_n;  // prefix over the lanes: where this lane's staged entries go
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t2 = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t2;
-  }
-  const int ne = __shfl_sync(0xffffffffu, incl, 31);
-  wkey = __reduce_max_sync(0xffffffffu, wkey);
-  if (ne > kTailStageCap) return res;
-  {
-    int wpos = incl - mine_n;
-#pragma unroll
-    for (int j = 0; j < kTailCtaRegs; ++j) {
-      const int n = (int)((cnts >> (4 * j)) & 15u);
-      const int c = j * 32 + lane;
-      for (int i = 0; i < n; ++i) st[wpos++] = make_uint2(h16_bits_key(__half_as_ushort(recs[c].v[i])), (uint32_t)recs[c].t[i]);
-    }
-  }
+  __syncwarp();
+  if (__any_sync(0xffffffffu, spill)) return res;
+  const int ne = *stage_n;
+  const uint32_t wkey = __reduce_max_sync(0xffffffffu, h16_key(wmax));
   __syncwarp();
   if (a.dbg && b == 0 && lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); a.dbg[7] = t_; }
   // 5. t_k: the K-th largest staged value (every staged value survives when fewer than K exist)
@@ -475,12 +486,12 @@ static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a,
     if (ne <= 128) {  // the usual case: a handful of keys per lane, kept in registers
       uint32_t sk[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) sk[j] = j * 32 + lane < ne ? st[j * 32 + lane].x : 0u;
+      for (int j = 0; j < 4; ++j) sk[j] = j * 32 + lane < ne ? h16_bits_key(st[j * 32 + lane].x) : 0u;
       tk = warp_kth_largest_reg(sk, K);
     } else {
       uint32_t sk[kTailStageCap / 32];
 #pragma unroll
-      for (int j = 0; j < kTailStageCap / 32; ++j) sk[j] = j * 32 + lane < ne ? st[j * 32 + lane].x : 0u;
+      for (int j = 0; j < kTailStageCap / 32; ++j) sk[j] = j * 32 + lane < ne ? h16_bits_key(st[j * 32 + lane].x) : 0u;
       tk = warp_kth_largest_reg(sk, K);
     }
   }
@@ -493,11 +504,11 @@ static __device__ __noinline__ TailRowResult tail_resolve_row(const TailArgs& a,
   for (int i0 = 0; i0 < ne; i0 += 32) {
     const int i = i0 + lane;
     const uint2 e = i < ne ? st[i] : make_uint2(0u, 0u);
-    const bool keep = i < ne && e.x >= tk;
+    const bool keep = i < ne && h16_bits_key(e.x) >= tk;
     const unsigned mask = __ballot_sync(0xffffffffu, keep);
     const int pos = nsv + __popc(mask & lt);
     if (keep && pos < kTailSurvCap) {
-      cv[pos] = h16_key_to_float(e.x);
+      cv[pos] = __half2float(__ushort_as_half((unsigned short)e.x));
       ct[pos] = (int)((long long)(int)e.y + voff);
     }
     nsv += __popc(mask);
@@ -607,15 +618,6 @@ __device__ __forceinline__ void lm_head_tail(const LmHeadParams& p, const RowMet
   __syncthreads();
   dbg_stamp(p, 4);
   if (threadIdx.x == 0) *p.ticket = 0u;  // ready for the next launch on this handle
-}
-
-// ---- sorted lists of the largest logits ------------------------------------------------------------
-// `e` holds n entries in descending order of value; (v, t) goes in if v > e[n-1].v, the last falls out.
-__device__ __forceinline__ void list_insert(Cand* e, int n, float v, int t) {
-  if (!(v > e[n - 1].v)) return;
-  int i = n - 1;
-  while (i > 0 && v > e[i - 1].v) { e[i] = e[i - 1]; --i; }
-  e[i] = Cand{v, t};
 }
 
 }  // namespace vqk
