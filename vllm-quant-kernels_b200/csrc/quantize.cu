@@ -134,16 +134,16 @@ __global__ void k_act_int8(const T* __restrict__ x, long long ldx, int H, int8_t
 
 // Decode-sized batches: absmax and quantisation by ONE block (no memset, no second launch); the
 // same arithmetic as the pair above.
-constexpr long long kActInt8OneBlock = 131072;  // elements (B * H) the single block takes
+constexpr long long kActInt8OneBlock = 32768;  // elements (B * H) the single block takes (beyond: one block per row is faster)
 template <typename T>
 __global__ void __launch_bounds__(1024) k_act_int8_one(const T* __restrict__ x, long long ldx, int B, int H,
                                                        int8_t* __restrict__ out, float* xs) {
   pdl_launch_dependents();
   __shared__ float red[32];
   __shared__ float s_scale;
-  const long long n = (long long)B * H;
   float m = 0.f;
-  for (long long i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, fabsf(ld_f32(x + (i / H) * ldx, i % H)));
+  for (int r = 0; r < B; ++r)
+    for (int c = threadIdx.x; c < H; c += blockDim.x) m = fmaxf(m, fabsf(ld_f32(x + (long long)r * ldx, c)));
   m = block_max(m, red);
   if (threadIdx.x == 0) {
     s_scale = fmaxf(m / 127.0f, 1e-12f);
@@ -152,10 +152,11 @@ __global__ void __launch_bounds__(1024) k_act_int8_one(const T* __restrict__ x, 
   }
   __syncthreads();
   const float s = s_scale;
-  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = rintf(ld_f32(x + (i / H) * ldx, i % H) / s);
-    out[i] = (int8_t)(int)fminf(fmaxf(v, -127.0f), 127.0f);
-  }
+  for (int r = 0; r < B; ++r)
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      const float v = rintf(ld_f32(x + (long long)r * ldx, c) / s);
+      out[(long long)r * H + c] = (int8_t)(int)fminf(fmaxf(v, -127.0f), 127.0f);
+    }
 }
 
 // ---- host dispatch ------------------------------------------------------------------------

@@ -29,6 +29,8 @@
 // All logits on this path are fp16 values, so their order is the order of 16-bit keys.
 #pragma once
 
+#include <type_traits>
+
 #include "lm_head.cuh"
 #include "peer_exchange.cuh"
 
@@ -177,15 +179,23 @@ static __device__ __noinline__ int warp_topk_inplace(float* v, int* t, int n, in
   low = __all_sync(0xffffffffu, low);
   float thr;  // the K-th largest value; entries >= it survive (float compare: -0 ties with +0)
   if (low && n <= 512) {  // the usual case: fp16 logits, a few per lane - select on registers, 16-bit keys
-    uint32_t key[16];
+    // (as few registers as the count needs: a selection round costs in proportion to them)
+    auto select = [&](auto rtag) {
+      constexpr int R = decltype(rtag)::value;
+      uint32_t key[R];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) key[j] = j * 32 + lane < n ? h16_key(v[j * 32 + lane]) : 0u;
-    int fin = 0;
+      for (int j = 0; j < R; ++j) key[j] = j * 32 + lane < n ? h16_key(v[j * 32 + lane]) : 0u;
+      int fin = 0;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) fin += (key[j] >= kKeyLowestFinite);
-    fin = __reduce_add_sync(0xffffffffu, fin);
-    // (-inf entries can only come from an all -inf shard; with fewer than K finite values all of them survive)
-    const uint32_t k16 = fin >= K ? warp_kth_largest_reg(key, K) : kKeyLowestFinite;
+      for (int j = 0; j < R; ++j) fin += (key[j] >= kKeyLowestFinite);
+      fin = __reduce_add_sync(0xffffffffu, fin);
+      // (-inf entries can only come from an all -inf shard; with fewer than K finite values all of them survive)
+      return fin >= K ? warp_kth_largest_reg(key, K) : kKeyLowestFinite;
+    };
+    uint32_t k16;
+    if (n <= 128) k16 = select(std::integral_constant<int, 4>{});
+    else if (n <= 256) k16 = select(std::integral_constant<int, 8>{});
+    else k16 = select(std::integral_constant<int, 16>{});
     thr = h16_key_to_float(k16);
   } else {
     thr = key_f32(warp_kth_largest_key([&](int i) { return f32_key(v[i]); }, n, K, 31, low ? 13 : 0, lane));
