@@ -274,6 +274,23 @@ int64_t vqk_lm_head_step_sharded_workspace_bytes(const vqk_lm_head* h, int64_t B
 int vqk_lm_head_step_sharded(vqk_lm_head* h, vqk_peer* peer, const void* x, int x_dtype, int64_t B, int64_t ldx,
                              const void* bias, const vqk_sample_params* sp, int64_t* tokens, float* scores,
                              void* workspace, int64_t workspace_bytes, void* stream);
+/* One decode step from HOST memory (no counterpart in the reference, whose hooks get device
+ * tensors from vLLM): `x_host` [B, H] (x_dtype, rows contiguous) and the per-row arrays of
+ * `sp_host` (HOST pointers; null where vqk_sample_params allows it) are staged through a pinned
+ * buffer the handle owns and travel in ONE host-to-device copy; the step runs as
+ * vqk_lm_head_forward would (vqk_lm_head_step_sharded when `peer` is given: sp_host then carries
+ * this rank's vocab_offset and the global vocab_total); the tokens land in `tokens_host` [B], and the
+ * call returns when they are there.  Without `scores_host` the kernels write the tokens straight
+ * into mapped pinned memory and the host watches them arrive (bounded: then it falls back to a
+ * stream synchronise), which saves the device-to-host copy and the wake-up of a blocking wait;
+ * with `scores_host` [B] tokens and scores come back by one copy and a stream synchronise.
+ * `workspace`: device memory of vqk_lm_head_step_host_workspace_bytes(h, B) (or more).  The
+ * first call, and a call with a larger B than any before, allocate the staging buffers: not
+ * inside a stream capture.  `bias` is a device pointer, as in vqk_lm_head_forward. */
+int64_t vqk_lm_head_step_host_workspace_bytes(const vqk_lm_head* h, int64_t B);
+int vqk_lm_head_step_host(vqk_lm_head* h, vqk_peer* peer /* or NULL */, const void* x_host, int x_dtype, int64_t B,
+                          const void* bias, const vqk_sample_params* sp_host, int64_t* tokens_host,
+                          float* scores_host /* or NULL */, void* workspace, int64_t workspace_bytes, void* stream);
 int vqk_peer_exchange_finalize(vqk_peer* p, const void* records /* [B, VQK_RECORD_BYTES] device */, int64_t B,
                                const vqk_sample_params* sp, int64_t* tokens, float* scores, void* stream);
 int vqk_peer_destroy(vqk_peer* p);

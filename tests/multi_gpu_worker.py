@@ -68,6 +68,15 @@ def main():
             tok, sc = peer.exchange_finalize(rec, ph.local_args(sp))
             torch.cuda.synchronize()
             assert torch.equal(tok, ref_tok) and torch.equal(sc, ref_sc), ("peer records", rank, mode, list(kw))
+        # the same step from host tensors, one library call (vqk_lm_head_step_host with the peer handle)
+        spk = args(top_k=np.full(B, 50, np.int32), top_p=np.full(B, 0.9, np.float32))
+        ref_tok, _ = full.sample(x, spk)
+        sp_cpu = LH.SamplingArgs(spk.temperature.cpu(), spk.seeds.cpu(), spk.top_k.cpu(), spk.top_p.cpu(), None, 0, V)
+        th = torch.empty(B, dtype=torch.int64)
+        run = VocabShardedLMHead(mine, a, V, peer=peer).host_stepper(x.cpu(), sp_cpu, th)
+        for _ in range(3):
+            assert run().tolist() == ref_tok.cpu().tolist(), ("host step", rank, mode, th.tolist(), ref_tok.tolist())
+        torch.cuda.synchronize()
         # a batch above 16 rows: the full-row sampler kernel does the exchange
         xb = torch.randn(24, H, generator=torch.Generator().manual_seed(11)).half().to(dev)
         rngb = np.random.default_rng(5)

@@ -160,6 +160,12 @@ struct vqk_lm_head {
   int ticket_slot;
   unsigned long long* dbg;
   float soft_cap, out_scale;
+  // vqk_lm_head_step_host: pinned (mapped) host staging [inputs | tokens | scores] and its device mirror
+  uint8_t* host_stage;
+  uint8_t* dev_stage;
+  long long* host_tokens_dev;  // device address of the mapped token words
+  size_t stage_in_cap;  // bytes of the input part
+  long long stage_rows; // rows the output part holds
 };
 
 extern "C" int vqk_version(void) { return VQK_VERSION; }
@@ -210,6 +216,7 @@ extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, i
   h->mode = mode; h->q = (const uint8_t*)q; h->scales = scales; h->V = V; h->H = H;
   h->ev_start = nullptr; h->ev_stop = nullptr; h->dbg = nullptr;
   h->soft_cap = 0.f; h->out_scale = 1.f;
+  h->host_stage = nullptr; h->dev_stage = nullptr; h->stage_in_cap = 0; h->stage_rows = 0;
   static unsigned int next_slot = 0;
   h->ticket_slot = (int)(__atomic_fetch_add(&next_slot, 1u, __ATOMIC_RELAXED) % kTicketSlots);
   *out = h;
@@ -217,6 +224,10 @@ extern "C" int vqk_lm_head_create(int mode, const void* q, const void* scales, i
 }
 
 extern "C" int vqk_lm_head_destroy(vqk_lm_head* h) {
+  if (h) {
+    if (h->host_stage) cudaFreeHost(h->host_stage);
+    if (h->dev_stage) cudaFree(h->dev_stage);
+  }
   delete h;
   return VQK_OK;
 }
@@ -698,6 +709,90 @@ extern "C" int vqk_lm_head_step_sharded(vqk_lm_head* h, vqk_peer* peer, const vo
   void* records = (uint8_t*)workspace + base;
   return lm_head_forward_impl(h, x, x_dtype, B, ldx, bias, nullptr, 0, sp, tokens, scores, records, peer, workspace,
                               base, stream);
+}
+
+// ---- host-buffer step -----------------------------------------------------------------------------
+extern "C" int64_t vqk_lm_head_step_host_workspace_bytes(const vqk_lm_head* h, int64_t B) {
+  return vqk_lm_head_step_sharded_workspace_bytes(h, B);
+}
+
+static inline size_t pad16(size_t n) { return (n + 15) & ~(size_t)15; }
+constexpr long long kHostTokenPending = (long long)0x8000000000000000ull;  // no token has this value
+
+extern "C" int vqk_lm_head_step_host(vqk_lm_head* h, vqk_peer* peer, const void* x_host, int x_dtype, int64_t B,
+                                     const void* bias, const vqk_sample_params* sp_host, int64_t* tokens_host,
+                                     float* scores_host, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!h || !x_host || !sp_host || !tokens_host || B <= 0) return VQK_ERR_INVALID;
+  if (x_dtype != VQK_F16 && x_dtype != VQK_BF16) return VQK_ERR_INVALID;
+  cudaStream_t st = (cudaStream_t)stream;
+  // staging layout: x | temperature | seeds | top_k | top_p | topk_threshold (absent arrays take no room)
+  const size_t xb = pad16((size_t)B * h->H * 2), ab = pad16((size_t)B * 4);
+  const void* arr[5] = {sp_host->temperature, sp_host->seeds, sp_host->top_k, sp_host->top_p, sp_host->topk_threshold};
+  size_t off[5], in_bytes = xb;
+  for (int i = 0; i < 5; ++i) {
+    off[i] = in_bytes;
+    if (arr[i]) in_bytes += ab;
+  }
+  if (in_bytes > h->stage_in_cap || B > h->stage_rows) {  // (re)allocate: first call, or a larger batch
+    VQK_CUDA(cudaStreamSynchronize(st));
+    if (h->host_stage) cudaFreeHost(h->host_stage);
+    if (h->dev_stage) cudaFree(h->dev_stage);
+    h->host_stage = nullptr; h->dev_stage = nullptr; h->stage_in_cap = 0; h->stage_rows = 0;
+    const size_t cap = pad16(xb + 5 * ab);
+    VQK_CUDA(cudaHostAlloc((void**)&h->host_stage, cap + pad16((size_t)B * 8) + pad16((size_t)B * 4), cudaHostAllocMapped));
+    VQK_CUDA(cudaMalloc((void**)&h->dev_stage, cap + pad16((size_t)B * 8) + pad16((size_t)B * 4)));
+    h->stage_in_cap = cap;
+    h->stage_rows = B;
+    void* dp = nullptr;
+    VQK_CUDA(cudaHostGetDevicePointer(&dp, h->host_stage + cap, 0));
+    h->host_tokens_dev = reinterpret_cast<long long*>(dp);
+  }
+  uint8_t* hs = h->host_stage;
+  memcpy(hs, x_host, (size_t)B * h->H * 2);
+  for (int i = 0; i < 5; ++i)
+    if (arr[i]) memcpy(hs + off[i], arr[i], (size_t)B * 4);
+  volatile long long* tok_pinned = reinterpret_cast<volatile long long*>(hs + h->stage_in_cap);
+  float* sc_pinned = reinterpret_cast<float*>(hs + h->stage_in_cap + pad16((size_t)h->stage_rows * 8));
+  VQK_CUDA(cudaMemcpyAsync(h->dev_stage, hs, in_bytes, cudaMemcpyHostToDevice, st));
+  vqk_sample_params sp = *sp_host;
+  const uint8_t* ds = h->dev_stage;
+  sp.temperature = arr[0] ? reinterpret_cast<const float*>(ds + off[0]) : nullptr;
+  sp.seeds = arr[1] ? reinterpret_cast<const int32_t*>(ds + off[1]) : nullptr;
+  sp.top_k = arr[2] ? reinterpret_cast<const int32_t*>(ds + off[2]) : nullptr;
+  sp.top_p = arr[3] ? reinterpret_cast<const float*>(ds + off[3]) : nullptr;
+  sp.topk_threshold = arr[4] ? reinterpret_cast<const float*>(ds + off[4]) : nullptr;
+  const bool watch = scores_host == nullptr;
+  int64_t* tok_out;
+  float* sc_out = nullptr;
+  if (watch) {
+    // the kernels store every token straight into the mapped pinned words the host watches
+    for (int64_t b = 0; b < B; ++b) tok_pinned[b] = kHostTokenPending;
+    tok_out = reinterpret_cast<int64_t*>(h->host_tokens_dev);
+  } else {
+    tok_out = reinterpret_cast<int64_t*>(h->dev_stage + h->stage_in_cap);
+    sc_out = reinterpret_cast<float*>(h->dev_stage + h->stage_in_cap + pad16((size_t)h->stage_rows * 8));
+  }
+  int rc;
+  if (peer) rc = vqk_lm_head_step_sharded(h, peer, ds, x_dtype, B, h->H, bias, &sp, tok_out, sc_out, workspace, workspace_bytes, stream);
+  else rc = vqk_lm_head_forward(h, ds, x_dtype, B, h->H, bias, nullptr, 0, &sp, tok_out, sc_out, nullptr, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (watch) {
+    // bounded watch (about two seconds of polls), then the ordinary blocking wait
+    bool all = false;
+    for (long long it = 0; it < (1LL << 28) && !all; ++it) {
+      all = true;
+      for (int64_t b = 0; b < B; ++b)
+        if (tok_pinned[b] == kHostTokenPending) { all = false; break; }
+    }
+    if (!all) VQK_CUDA(cudaStreamSynchronize(st));
+    for (int64_t b = 0; b < B; ++b) tokens_host[b] = tok_pinned[b];
+  } else {
+    const size_t out_bytes = pad16((size_t)h->stage_rows * 8) + (size_t)B * 4;
+    VQK_CUDA(cudaMemcpyAsync(hs + h->stage_in_cap, h->dev_stage + h->stage_in_cap, out_bytes, cudaMemcpyDeviceToHost, st));
+    VQK_CUDA(cudaStreamSynchronize(st));
+    for (int64_t b = 0; b < B; ++b) { tokens_host[b] = tok_pinned[b]; scores_host[b] = sc_pinned[b]; }
+  }
+  return VQK_OK;
 }
 
 extern "C" int64_t vqk_lm_head_step_sharded_workspace_bytes(const vqk_lm_head* h, int64_t B) {

@@ -169,6 +169,22 @@ class VocabShardedLMHead:
         return SamplingArgs(sp.temperature, sp.seeds, sp.top_k, sp.top_p, sp.topk_threshold,
                             vocab_offset=self.vocab_start, vocab_total=self.vocab_total)
 
+    def step_host(self, x_host: torch.Tensor, sp_host: SamplingArgs, tokens_host: torch.Tensor,
+                  bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The sharded step from HOST tensors in one library call (`LMHeadShard.step_host` with this
+        rank's vocab offset and the peer handle); peer-memory exchange only.  Rows the records
+        cannot carry come back as -1, as with ``unresolved="leave"``."""
+        if self.peer is None:
+            raise RuntimeError("step_host needs the peer-memory exchange (VqkPeer)")
+        return self.shard.step_host(x_host, self.local_args(sp_host), tokens_host, peer_handle=self.peer._h, bias=bias)
+
+    def host_stepper(self, x_host: torch.Tensor, sp_host: SamplingArgs, tokens_host: torch.Tensor,
+                     bias: Optional[torch.Tensor] = None):
+        """`step_host` bound to fixed host tensors (`LMHeadShard.host_stepper`)."""
+        if self.peer is None:
+            raise RuntimeError("host_stepper needs the peer-memory exchange (VqkPeer)")
+        return self.shard.host_stepper(x_host, self.local_args(sp_host), tokens_host, peer_handle=self.peer._h, bias=bias)
+
     def step(self, hidden_states: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None,
              unresolved: str = "leave"):
         """(tokens int64 [B], scores fp32 [B]), identical on every rank.

@@ -33,6 +33,7 @@ SYMBOLS = (
     "vqk_comm_unique_id", "vqk_comm_create", "vqk_comm_allgather", "vqk_comm_destroy",
     "vqk_peer_create", "vqk_peer_connect", "vqk_peer_connect_pointers", "vqk_peer_local_buffer",
     "vqk_peer_set_wait_limit", "vqk_lm_head_step_sharded_workspace_bytes", "vqk_lm_head_step_sharded",
+    "vqk_lm_head_step_host_workspace_bytes", "vqk_lm_head_step_host",
     "vqk_peer_exchange_finalize", "vqk_peer_destroy",
 )
 
@@ -106,6 +107,11 @@ def lib() -> ctypes.CDLL:
     L.vqk_lm_head_step_sharded_workspace_bytes.argtypes = [c_void_p, c_int64]
     L.vqk_lm_head_step_sharded.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, POINTER(SampleParams), c_void_p, c_void_p,
+        c_void_p, c_int64, c_void_p]
+    L.vqk_lm_head_step_host_workspace_bytes.restype = c_int64
+    L.vqk_lm_head_step_host_workspace_bytes.argtypes = [c_void_p, c_int64]
+    L.vqk_lm_head_step_host.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, POINTER(SampleParams), c_void_p, c_void_p,
         c_void_p, c_int64, c_void_p]
     for name in SYMBOLS:
         fn = getattr(L, name)

@@ -302,6 +302,75 @@ class LMHeadShard:
                                                   ws.data_ptr(), n, _stream(x2)))
         return tokens, scores
 
+    def _host_step_args(self, x_host, sp_host, tokens_host, scores_host, peer_handle, bias, stream):
+        assert x_host.dim() == 2 and x_host.shape[1] == self.H and x_host.dtype in (torch.float16, torch.bfloat16)
+        assert not x_host.is_cuda and x_host.is_contiguous()
+        B = x_host.shape[0]
+        assert tokens_host.dtype == torch.int64 and tokens_host.shape == (B,) and not tokens_host.is_cuda
+        if scores_host is not None:
+            assert scores_host.dtype == torch.float32 and scores_host.shape == (B,) and not scores_host.is_cuda
+
+        def hp(t, dt, name):
+            if t is None:
+                return None
+            if t.is_cuda or t.dtype != dt or t.shape != (B,) or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous CPU {dt} tensor of shape ({B},)")
+            return t.data_ptr()
+        total = self.V if sp_host.vocab_total is None else int(sp_host.vocab_total)
+        spc = _ffi.SampleParams(
+            hp(sp_host.temperature, torch.float32, "temperature"), hp(sp_host.seeds, torch.int32, "seeds"),
+            hp(sp_host.top_k, torch.int32, "top_k"), hp(sp_host.top_p, torch.float32, "top_p"),
+            hp(sp_host.topk_threshold, torch.float32, "topk_threshold"), int(sp_host.vocab_offset), total)
+        if bias is not None:
+            bias = bias.to(torch.float16).contiguous()
+        L = _ffi.lib()
+        key = ("host", B)
+        n = self._ws_bytes.get(key)
+        if n is None:
+            with torch.cuda.device(self.device):
+                n = int(L.vqk_lm_head_step_host_workspace_bytes(self._h, B))
+            if n < 0:
+                _ffi.check(n)
+            self._ws_bytes[key] = n
+        ws = self._wsp.get(self.device, n)
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        args = (self._h, peer_handle, x_host.data_ptr(), _DT[x_host.dtype], B, _ptr(bias), ctypes.byref(spc),
+                tokens_host.data_ptr(), _ptr(scores_host), ws.data_ptr(), n, st)
+        keep = (x_host, sp_host, tokens_host, scores_host, bias, ws, spc)  # what the raw pointers refer to
+        return args, keep
+
+    def step_host(self, x_host: torch.Tensor, sp_host: "SamplingArgs", tokens_host: torch.Tensor,
+                  scores_host: Optional[torch.Tensor] = None, peer_handle=None, bias: Optional[torch.Tensor] = None,
+                  stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """One decode step from HOST tensors in ONE library call (`vqk_lm_head_step_host`):
+        `x_host` [B, H] fp16 / bf16 and the arrays of `sp_host` are CPU tensors (any memory; the
+        library stages them through a pinned buffer of its own), `tokens_host` is a CPU int64
+        tensor [B] that receives the tokens.  Returns `tokens_host` when the tokens are in it.
+        Without `scores_host` the kernels write the tokens straight into mapped host memory and
+        the call watches them arrive; with it (CPU fp32 [B]) both come back by a copy and a
+        stream synchronise.  `peer_handle`: a connected vqk_peer for a vocab-sharded step."""
+        args, _keep = self._host_step_args(x_host, sp_host, tokens_host, scores_host, peer_handle, bias, stream)
+        with torch.cuda.device(self.device):
+            _ffi.check(_ffi.lib().vqk_lm_head_step_host(*args))
+        return tokens_host
+
+    def host_stepper(self, x_host: torch.Tensor, sp_host: "SamplingArgs", tokens_host: torch.Tensor,
+                     scores_host: Optional[torch.Tensor] = None, peer_handle=None,
+                     bias: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
+        """`step_host` bound to fixed host tensors: a decode loop that refills `x_host` and the
+        sampling arrays in place calls the returned function once per step and reads
+        `tokens_host`; the argument checks and the workspace lookup are done once, here.  The
+        caller keeps this device current (`torch.cuda.set_device`)."""
+        args, keep = self._host_step_args(x_host, sp_host, tokens_host, scores_host, peer_handle, bias, stream)
+        fn, check = _ffi.lib().vqk_lm_head_step_host, _ffi.check
+
+        def run(_keep=keep):
+            rc = fn(*args)
+            if rc:
+                check(rc)
+            return tokens_host
+        return run
+
     def shard_records(self, x: torch.Tensor, sp: SamplingArgs, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """lm_head + local sampling stage of a vocab-sharded step: uint8 [B, 1024]
         exchange records to be all-gathered and passed to `finalize_records`."""
