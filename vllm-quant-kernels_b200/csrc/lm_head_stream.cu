@@ -26,6 +26,8 @@
 
 namespace vqk {
 
+// weight loads: evict-first (the read-only no-allocate form measured the same, and it too needs the L1:
+// see stream_smem_total)
 __device__ __forceinline__ uint4 ldg_stream16(const uint8_t* p) {
   return __ldcs(reinterpret_cast<const uint4*>(p));
 }
@@ -119,11 +121,17 @@ __device__ __forceinline__ void col_compact(Cand* buf, ColCtl* ctl, int lane) {
   }
   __syncwarp();
 }
-// (the sampler tail reuses the buffer once the main loop is over: one warp's scratch per batch row)
+// (the sampler tail reuses the buffer once the main loop is over: one warp's scratch per batch row, as
+// far as kStreamTailSmemCap allows - with fewer it takes the rows in rounds.  Shared memory is taken
+// from the L1, and the weight stream needs the L1: its loads in flight occupy lines there.  Measured
+// at batch 1: 119 us per launch with up to 180 KB of shared memory, 181 us with 200 KB or more; at batch
+// 16 (two column tiles, 150 KB for the main loop) 135 us, but 172 us with 186 KB.)
+constexpr size_t kStreamTailSmemCap = 128 * 1024;  // eight rows at a time
 __host__ __device__ inline size_t stream_smem_total(int mode, int K, int NT, int B) {
   const size_t main_loop = stream_xfrag_bytes(mode, K, NT) + stream_sx_bytes(mode, K, NT) + stream_red_bytes(NT) +
                            (size_t)NT * 8 * sizeof(RowMeta) + stream_tlist_bytes(NT) + stream_win_bytes(NT) + kStreamBarBytes;
-  const size_t tail = tail_smem_bytes(B < NT * 8 ? B : NT * 8);
+  size_t tail = tail_smem_bytes(B < NT * 8 ? B : NT * 8);
+  if (tail > kStreamTailSmemCap) tail = kStreamTailSmemCap;
   return main_loop > tail ? main_loop : tail;
 }
 size_t stream_smem_bytes(int mode, int K, int NT) { return stream_smem_total(mode, K, NT, NT * 8); }
@@ -665,6 +673,10 @@ int stream_error_clear() { return clear_stream_error(); }
 template <int MODE, int NT, int U, bool EVEN>
 static int launch_stream(const LmHeadParams& p, int grid, cudaStream_t st) {
   size_t smem = stream_smem_total(MODE, p.K, NT, p.B);
+  {  // measurement aid: VQK_STREAM_SMEM_KB asks for at least that much shared memory (the L1 shrinks accordingly)
+    static const size_t want = [] { const char* e = getenv("VQK_STREAM_SMEM_KB"); return e ? (size_t)atoi(e) * 1024 : (size_t)0; }();
+    if (want > smem && want <= 226 * 1024) smem = want;
+  }
   static size_t configured[64] = {};  // per device: largest opt-in so far for this instantiation
   int dev = 0;
   VQK_CUDA(cudaGetDevice(&dev));
