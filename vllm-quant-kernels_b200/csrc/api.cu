@@ -86,7 +86,7 @@ struct LmHeadWs {
 // Zero at load; the last CTA of every launch puts its slot back to zero.  In host code the array's
 // name is only a stand-in: the device address is looked up once per device.
 constexpr int kTicketSlots = 256;
-static __device__ unsigned int g_tickets[kTicketSlots];
+static __device__ unsigned int g_tickets[kTicketSlots * 2];  // per slot: the end-of-kernel ticket, the streaming kernel's tile counter
 static unsigned int* g_tickets_ptr[64];
 static std::mutex g_symbol_mu;  // the once-per-device address look-ups may come from several host threads
 static int ticket_base(unsigned int** out) {
@@ -198,6 +198,11 @@ extern "C" int vqk_device_error_clear(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return VQK_ERR_CUDA;
   if (stream_error_clear() || umma_error_clear() || umma_mx_error_clear()) return VQK_ERR_CUDA;
   VQK_CUDA(cudaMemcpyToSymbol(g_peer_error, &zero, sizeof(int)));
+  {  // a launch that gave up may have left its ticket or tile counter behind
+    void* tp = nullptr;
+    VQK_CUDA(cudaGetSymbolAddress(&tp, g_tickets));
+    VQK_CUDA(cudaMemset(tp, 0, sizeof(unsigned int) * kTicketSlots * 2));
+  }
   return VQK_OK;
 }
 
@@ -335,9 +340,15 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   const bool fuse_tail = tail_mode && tail_here && sp && B <= kTailMaxBatch && B <= maxcols && nslices <= 1024;
   unsigned int* tickets = nullptr;
   int* error_word = nullptr;
-  if (fuse_tail) {
+  // the streaming kernel hands its tiles out dynamically beyond the first two rounds (VQK_STREAM_DYNAMIC=0:
+  // static rounds, for A/B runs); the counter sits next to the handle's ticket and is reset by the last CTA
+  static const bool dynamic_tiles = [] { const char* e = getenv("VQK_STREAM_DYNAMIC"); return !(e && atoi(e) == 0); }();
+  const bool want_counter = !use_umma && dynamic_tiles;
+  if (fuse_tail || want_counter) {
     rc = ticket_base(&tickets);
     if (rc) return rc;
+  }
+  if (fuse_tail) {
     rc = peer_error_word(&error_word);
     if (rc) return rc;
   }
@@ -385,13 +396,17 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
       if (fuse_tail) {
         p.fuse_tail = tail_mode == 2 ? 2 : 1;
         p.lists = ws.lists;
-        p.ticket = tickets + h->ticket_slot;
+        p.ticket = tickets + 2 * h->ticket_slot;
         p.error = error_word;
         p.row_flag = ws.row_flag;
         p.tokens = (long long*)tokens; p.scores = scores; p.records = (uint8_t*)records;
         p.single_shard = (tokens && !peer) ? 1 : 0;
         p.peer = pt;
       }
+    }
+    if (want_counter) {
+      p.ticket = tickets + 2 * h->ticket_slot;
+      p.tile_counter = tickets + 2 * h->ticket_slot + 1;
     }
     rc = use_umma ? (mx_mode ? launch_lm_head_umma_mx(mode, p, grid, st) : launch_lm_head_umma(mode, p, grid, st))
                    : launch_lm_head_stream(mode, p, grid, st);

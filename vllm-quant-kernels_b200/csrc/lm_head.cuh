@@ -56,6 +56,7 @@ struct LmHeadParams {
   int fuse_tail;
   CtaList* lists;        // [B][gridDim.x] what every CTA hands to the tail (decode-sized batches); null: no tail
   unsigned int* ticket;  // device counter, zero between launches
+  unsigned int* tile_counter;  // streaming kernel: tiles handed out beyond the first two rounds (zero between launches); null: static rounds
   int* error;            // device error word, set when the tail's bounded wait for the grid runs out
   int* row_flag;         // [B] written by the tail: 1 = the row still needs the full-row kernel
   long long* tokens;     // outputs of the tail (as SelectParams)

@@ -72,7 +72,7 @@ __host__ __device__ inline size_t stream_sx_bytes(int mode, int K, int NT) {
 __host__ __device__ inline size_t stream_red_bytes(int NT) { return (size_t)2 * kStreamWarps * NT * 128 * 4; }
 // per warp group, batch column and tile row: running Gumbel (or greedy) winner of rows without top-k / top-p
 __host__ __device__ inline size_t stream_win_bytes(int NT) { return (size_t)kGroups * NT * 8 * 16 * sizeof(Cand); }
-constexpr size_t kStreamBarBytes = (size_t)(4 * kGroups + 1) * 8;  // full / free barriers of the partial-sum buffers, abort flag
+constexpr size_t kStreamBarBytes = (size_t)(4 * kGroups + 1) * 8 + (size_t)kGroups * 8 * 4;  // full / free barriers of the partial-sum buffers, abort flag; per group four (tag, tile) slots of the tile hand-out
 // Per warp group and batch column (sampler, top-k rows): the largest logits of the group's slice.
 // A logit above the column's threshold is APPENDED to a small buffer (every passing lane at once, no
 // order kept); when another pass might not fit, the buffer is cut back to its kListM largest and the
@@ -151,6 +151,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   uint64_t* fullb = reinterpret_cast<uint64_t*>(swin + (size_t)kGroups * NT * 8 * 16);  // [group][buffer]: partial sums parked
   uint64_t* freeb = fullb + 2 * kGroups;                                           // [group][buffer]: partial sums read
   volatile int* abort_flag = reinterpret_cast<volatile int*>(freeb + 2 * kGroups);
+  volatile int* seq_tag = reinterpret_cast<volatile int*>(freeb + 2 * kGroups + 1);  // [group][4]: 2 m = tile m is being fetched, 2 m + 1 = seq_val holds it
+  volatile int* seq_val = seq_tag + kGroups * 4;                                       // [group][4]
 
   dbg_stamp(p, 0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -170,6 +172,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
       mbar_init(&freeb[i], 128);
     }
     *abort_flag = 0;
+    // slot s is free for tile m (m & 3 == s) when it says "tile m - 4 was published"; tiles 0 and 1 are static
+    for (int i = 0; i < kGroups * 4; ++i) seq_tag[i] = (i & 3) < 2 ? 2 * (i & 3) + 1 : 2 * ((i & 3) - 4) + 1;
   }
 
   const int ntiles = (V + 15) / 16;
@@ -332,6 +336,47 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   const int rest_tile = main_end + (int)blockIdx.x;  // this CTA's first leftover tile
   const bool rest_have = split_rest && rest_tile < ntiles;
   bool rest_loaded = false;
+  // Tile hand-out.  A group's first two tiles are the static round-robin ones; beyond them, when the launch
+  // has a tile counter, groups take tiles as they get to them (the CTAs' streaming rates differ: their
+  // finishing times spread over 9 us with static rounds).  The m-th tile of a group is fetched (one
+  // atomicAdd) two tiles ahead by whichever of its warps gets there first, published through a shared
+  // slot a batch later, and read by every warp at the end of tile m - 1.
+  const bool dynamic = p.tile_counter != nullptr;
+  volatile int* gtag = seq_tag + group * 4;
+  volatile int* gval = seq_val + group * 4;
+  bool fetching = false;      // lane 0: an atomicAdd of mine is in flight for tile `fetch_seq`
+  int fetch_seq = 0, fetch_age = 0;
+  unsigned int fetched = 0;
+  auto publish_now = [&]() {
+    gval[fetch_seq & 3] = 2 * tstride + (int)fetched;
+    __threadfence_block();
+    gtag[fetch_seq & 3] = 2 * fetch_seq + 1;
+    fetching = false;
+  };
+  auto fetch_ahead = [&](int m) {  // at the start of tile m - 2
+    if (!dynamic || m < 2 || lane != 0) return;
+    if (fetching) publish_now();  // (one batch per tile: the earlier answer has not been passed on yet)
+    if (atomicCAS(const_cast<int*>(&gtag[m & 3]), 2 * (m - 4) + 1, 2 * m) == 2 * (m - 4) + 1) {
+      fetched = atomicAdd(p.tile_counter, 1u);
+      fetching = true;
+      fetch_seq = m;
+      fetch_age = 0;
+    }
+  };
+  auto publish = [&]() {  // at the top of every batch; acts one whole batch after fetch_ahead, when the counter's answer has arrived
+    if (fetching && fetch_age++ >= 1) publish_now();
+  };
+  auto tile_of = [&](int m, int prev) -> int {  // the group's m-th tile (m >= 1), `prev` its (m - 1)-th
+    if (!dynamic || m < 2) return prev + tstride;
+    int v = main_end;  // nothing: when the wait runs out the warp stops taking tiles
+    if (lane == 0) {
+      for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (gtag[m & 3] == 2 * m + 1) { v = gval[m & 3]; break; }
+        if ((it & 255u) == 255u && *abort_flag) break;
+      }
+    }
+    return __shfl_sync(0xffffffffu, v, 0);
+  };
   int tile = blockIdx.x * kGroups + group, bi = 0;
   bool have = tile < main_end;
   if (have) {
@@ -516,13 +561,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   };
 
   // ---- main loop ---------------------------------------------------------------------------------
+  if (have) fetch_ahead(2);  // (behind the block barrier that follows the set-up of the hand-out slots)
   int tcount = 0;       // tiles this group has finished
   int ptile = 0;        // the previous one, whose epilogue is still due
   float prs = 1.f, pbias = 0.f;
   bool ok = true;
   while (have) {
+    publish();
     int ntile = tile, nbi = bi + 1;
-    if (nbi == nb) { nbi = 0; ntile = tile + tstride; }
+    if (nbi == nb) { nbi = 0; ntile = tile_of(tcount + 1, tile); }
     const bool nhave = ntile < main_end;
     // One set of registers, refilled unit by unit: as soon as a unit's MMAs have read it, the same
     // registers fetch that unit of the NEXT batch (also across tile boundaries), so U units per lane
@@ -561,6 +608,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
     ptile = this_tile;
     if (duty(tcount) < B) fetch_row_scale(this_tile, prs, pbias);  // in flight until the epilogue, a tile from now
     ++tcount;
+    if (have) fetch_ahead(tcount + 2);
   }
   // ---- leftover tiles: one per CTA and sub-round, K split over the sixteen warps -------------------------
   if (split_rest) {
@@ -663,6 +711,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
     }
     dbg_stamp(p, 2);
     if (p.fuse_tail) lm_head_tail(p, meta, smem, stream_smem_total(MODE, p.K, NT, B));
+  }
+  if (dynamic && !(p.do_sample && p.fuse_tail)) {
+    // no tail, so nobody has taken the ticket: the last CTA to finish puts the tile counter back to zero
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(p.ticket, 1u) == gridDim.x - 1) {
+        *p.tile_counter = 0u;
+        __threadfence();
+        *p.ticket = 0u;
+      }
+    }
   }
 }
 

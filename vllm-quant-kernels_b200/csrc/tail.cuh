@@ -627,7 +627,11 @@ __device__ __forceinline__ void lm_head_tail(const LmHeadParams& p, const RowMet
   lm_head_tail_rows(s_tail, scratch, nw);
   __syncthreads();
   dbg_stamp(p, 4);
-  if (threadIdx.x == 0) *p.ticket = 0u;  // ready for the next launch on this handle
+  if (threadIdx.x == 0) {  // ready for the next launch on this handle
+    if (p.tile_counter) *p.tile_counter = 0u;
+    __threadfence();
+    *p.ticket = 0u;
+  }
 }
 
 }  // namespace vqk
