@@ -110,6 +110,12 @@ typedef struct {
   const float* topk_threshold;
   int64_t vocab_offset; /* global id of local column 0 */
   int64_t vocab_total;  /* global vocabulary size (== V when not sharded) */
+  float* logprobs;      /* optional OUT [B] (device): raw log-softmax of the sampled token, i.e. of the
+                         * logits as given, before temperature / top-k / top-p (what vLLM reports by default;
+                         * the reference sends such batches back to vLLM, _sampler.py:158-169).  From the first
+                         * pass's per-slice maxima and sums of exponentials, no second pass over the row.
+                         * vqk_sample on a single shard only; every other entry point returns
+                         * VQK_ERR_UNSUPPORTED when it is set. */
 } vqk_sample_params;
 
 /* Per (rank, row) exchange record of a vocab-sharded step: 16-byte header

@@ -237,3 +237,16 @@ def resolve_candidates(values, tokens, T, seed, top_k=0, top_p=1.0):
     s = np.where(keep, (y + gumbel(int(seed), t)).astype(F32), F32(-np.inf))
     order = np.lexsort((t, -s.astype(np.float64)))     # highest score, then lowest token
     return int(t[order[0]]), F32(s[order[0]])
+
+
+def raw_logprob(logits, tokens):
+    """log-softmax of the given tokens over the logits as given (no temperature, no top-k / top-p):
+    what vLLM reports as the sampled token's log-probability by default
+    (vllm/v1/sample/sampler.py: `compute_logprobs` = log_softmax of the raw fp32 logits; the
+    reference's FusedSampler sends every batch that wants it back to vLLM,
+    src/vllm_quant_kernels/_sampler.py:158-169).  float64 arithmetic."""
+    l = np.asarray(logits, dtype=np.float64)
+    t = np.asarray(tokens, dtype=np.int64)
+    m = l.max(axis=1, keepdims=True)
+    lse = m[:, 0] + np.log(np.exp(l - m).sum(axis=1))
+    return (l[np.arange(l.shape[0]), t] - lse).astype(np.float32)

@@ -279,6 +279,7 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   if (!logits && !sp) return VQK_ERR_INVALID;
   if (sp && !tokens && !records) return VQK_ERR_INVALID;
   if (sp && sp->temperature && !sp->seeds) return VQK_ERR_INVALID;
+  if (sp && sp->logprobs) return VQK_ERR_UNSUPPORTED;  // stand-alone sampler only (vqk_sample)
   if (sp && tokens && !peer && (sp->vocab_total != h->V || sp->vocab_offset != 0)) return VQK_ERR_INVALID;
   if (sp && (sp->vocab_offset < 0 || sp->vocab_offset + h->V > sp->vocab_total || sp->vocab_total > 0x7fffffffLL))
     return VQK_ERR_INVALID;
@@ -440,6 +441,8 @@ struct SampleWs {
   float* slice_max;
   float* part_score;
   int* part_token;
+  float* lp_max;  // per-slice maximum and sum of exponentials (log-probability of the sampled token)
+  float* lp_sum;
   size_t total;
 };
 SampleWs carve_sample(void* base, long long B, int nslices) {
@@ -448,6 +451,8 @@ SampleWs carve_sample(void* base, long long B, int nslices) {
   w.slice_max = c.take<float>((size_t)B * nslices);
   w.part_score = c.take<float>((size_t)B * nslices);
   w.part_token = c.take<int>((size_t)B * nslices);
+  w.lp_max = c.take<float>((size_t)B * nslices);
+  w.lp_sum = c.take<float>((size_t)B * nslices);
   w.total = (c.off + 255) & ~(size_t)255;
   return w;
 }
@@ -477,14 +482,18 @@ extern "C" int vqk_sample(const void* logits, int dtype, int64_t B, int64_t V, i
   if ((uintptr_t)workspace & 255) return VQK_ERR_INVALID;
   cudaStream_t st = (cudaStream_t)stream;
   SampleDev sd = to_dev(sp);
-  rc = launch_slice_pass(logits, dtype, ld, (int)B, (int)V, sd, ws.slice_max, ws.part_score, ws.part_token, nslices, st);
+  if (sd.logprobs && !tokens) return VQK_ERR_UNSUPPORTED;  // the log-probability is of the merged token: single shard only
+  rc = launch_slice_pass(logits, dtype, ld, (int)B, (int)V, sd, ws.slice_max, ws.part_score, ws.part_token, nslices, st,
+                         sd.logprobs ? ws.lp_max : nullptr, sd.logprobs ? ws.lp_sum : nullptr);
   if (rc) return rc;
   SelectParams s{};
   s.logits = logits; s.dtype = dtype; s.ld = ld; s.V = (int)V; s.B = (int)B; s.sp = sd;
   s.slice_max = ws.slice_max; s.part_score = ws.part_score; s.part_token = ws.part_token; s.nslices = nslices;
   s.records = (uint8_t*)records; s.tokens = (long long*)tokens; s.scores = scores;
   s.single_shard = tokens ? 1 : 0;
-  return launch_select(s, st);
+  rc = launch_select(s, st);
+  if (rc || !sd.logprobs) return rc;
+  return launch_logprob(logits, dtype, ld, (int)B, (int)V, ws.lp_max, ws.lp_sum, nslices, (const long long*)tokens, sd.logprobs, st);
 }
 
 extern "C" int vqk_sample_static(const void* logits, int dtype, int64_t B, int64_t V, int64_t ld,
@@ -492,6 +501,7 @@ extern "C" int vqk_sample_static(const void* logits, int dtype, int64_t B, int64
   if (!logits || !sp || !tokens || B < 0 || V <= 0 || ld < V) return VQK_ERR_INVALID;
   if (dtype < VQK_F16 || dtype > VQK_F32) return VQK_ERR_INVALID;
   if (sp->temperature && !sp->seeds) return VQK_ERR_INVALID;
+  if (sp->logprobs) return VQK_ERR_UNSUPPORTED;  // the fixed scratch has no room for the per-slice sums
   if (B > VQK_STATIC_MAX_ROWS || V > VQK_STATIC_MAX_VOCAB) return VQK_ERR_TOO_LARGE;
   if (sp->vocab_total != V || sp->vocab_offset != 0) return VQK_ERR_INVALID;
   if (B == 0) return VQK_OK;
@@ -503,6 +513,7 @@ extern "C" int vqk_sample_static(const void* logits, int dtype, int64_t B, int64
 extern "C" int vqk_sample_finalize(const void* records, int G, int64_t B, const vqk_sample_params* sp, int64_t* tokens,
                                    float* scores, void* stream) {
   if (!records || !sp || !tokens || G <= 0 || G > 8 || B < 0) return VQK_ERR_INVALID;
+  if (sp->logprobs) return VQK_ERR_UNSUPPORTED;
   if (B > 65535) return VQK_ERR_TOO_LARGE;
   int rc = require_sm100();
   if (rc) return rc;
@@ -702,6 +713,7 @@ extern "C" int vqk_peer_exchange_finalize(vqk_peer* p, const void* records, int6
                                           int64_t* tokens, float* scores, void* stream) {
   if (!p || !p->connected || !records || !sp || !tokens || B < 0) return VQK_ERR_INVALID;
   if (sp->temperature && !sp->seeds) return VQK_ERR_INVALID;
+  if (sp->logprobs) return VQK_ERR_UNSUPPORTED;
   if (B > p->max_rows) return VQK_ERR_TOO_LARGE;
   int rc = require_sm100();
   if (rc) return rc;

@@ -137,7 +137,11 @@ struct SelectParams {
 
 // first pass over materialised logits: per-slice maxima / Gumbel winners (slices of 256 columns)
 int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, float* slice_max,
-                      float* part_score, int* part_token, int nslices, cudaStream_t st);
+                      float* part_score, int* part_token, int nslices, cudaStream_t st, float* lp_max = nullptr,
+                      float* lp_sum = nullptr);
+// log-softmax of the sampled tokens from the first pass's per-slice (max, sum of exponentials): lp_* [B][nslices]
+int launch_logprob(const void* logits, int dtype, long long ld, int B, int V, const float* lp_max, const float* lp_sum,
+                   int nslices, const long long* tokens, float* logprobs, cudaStream_t st);
 inline int slice_pass_nslices(long long V) { return (int)((V + 255) / 256); }
 // cluster-per-row selection: tau from slice maxima, candidate collection, final choice / record;
 // rows that do not fit the candidate scheme are resolved by an exact full-row pass inside
@@ -162,6 +166,7 @@ inline SampleDev to_dev(const vqk_sample_params* sp) {
   d.thr = sp->topk_threshold;
   d.vocab_offset = sp->vocab_offset;
   d.vocab_total = sp->vocab_total;
+  d.logprobs = sp->logprobs;
   return d;
 }
 inline SampleDev offset_rows(SampleDev d, long long b0) {

@@ -77,7 +77,8 @@ __device__ __forceinline__ unsigned long long mass_of(float y, float m) {
 template <typename T>
 __global__ void __launch_bounds__(256) k_slice_pass(const T* __restrict__ logits, long long ld, int V, SampleDev sp,
                                                    float* __restrict__ slice_max, float* __restrict__ part_score,
-                                                   int* __restrict__ part_token, int nslices) {
+                                                   int* __restrict__ part_token, int nslices, float* __restrict__ lp_max,
+                                                   float* __restrict__ lp_sum) {
   const int b = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const int slice = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -87,11 +88,14 @@ __global__ void __launch_bounds__(256) k_slice_pass(const T* __restrict__ logits
   const int c0 = slice * 256;
   float mx = -INFINITY;
   Best best{-INFINITY, 0x7fffffff};
+  float lv[8];  // the lane's logits, kept for the sum of exponentials (log-probability requested)
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int col = c0 + j * 32 + lane;
+    lv[j] = -INFINITY;
     if (col < V) {
       const float l = ldl(row, col);
+      lv[j] = l;
       if (m.flags & ROW_CAND) {
         mx = fmaxf(mx, l);
       } else {
@@ -111,6 +115,49 @@ __global__ void __launch_bounds__(256) k_slice_pass(const T* __restrict__ logits
     slice_max[(long long)b * nslices + slice] = mx;
     part_score[(long long)b * nslices + slice] = best.s;
     part_token[(long long)b * nslices + slice] = best.t;
+  }
+  if (lp_max) {  // per-slice maximum and sum of exp(logit - maximum) of EVERY row kind, for the log-softmax
+    float am = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) am = fmaxf(am, lv[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    float se = 0.f;
+    if (am > -INFINITY) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) se += expf(lv[j] - am);  // exp(-inf) = 0 for the lanes beyond the row
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+    if (lane == 0) {
+      lp_max[(long long)b * nslices + slice] = am;
+      lp_sum[(long long)b * nslices + slice] = se;
+    }
+  }
+}
+
+// log-softmax of the sampled token of every row: logit[token] - M - log(sum_s sum_s * exp(max_s - M)), one warp per row
+template <typename T>
+__global__ void __launch_bounds__(32) k_logprob(const T* __restrict__ logits, long long ld, int V, const float* __restrict__ lp_max,
+                                                const float* __restrict__ lp_sum, int nslices,
+                                                const long long* __restrict__ tokens, float* __restrict__ logprobs) {
+  const int b = blockIdx.x, lane = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = lane; s < nslices; s += 32) M = fmaxf(M, lp_max[(long long)b * nslices + s]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  float z = 0.f;
+  for (int s = lane; s < nslices; s += 32) {
+    const float ms = lp_max[(long long)b * nslices + s];
+    if (ms > -INFINITY) z += lp_sum[(long long)b * nslices + s] * expf(ms - M);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+  if (lane == 0) {
+    const long long t = tokens[b];
+    float lp = -INFINITY;
+    if (t >= 0 && t < V && M > -INFINITY) lp = ldl(logits + (long long)b * ld, (int)t) - M - logf(z);
+    logprobs[b] = lp;
   }
 }
 
@@ -675,11 +722,20 @@ __global__ void __launch_bounds__(1024) k_topk_threshold(const T* __restrict__ l
   }
 
 int launch_slice_pass(const void* logits, int dtype, long long ld, int B, int V, const SampleDev& sp, float* slice_max,
-                      float* part_score, int* part_token, int nslices, cudaStream_t st) {
+                      float* part_score, int* part_token, int nslices, cudaStream_t st, float* lp_max, float* lp_sum) {
   if (B == 0 || V == 0) return VQK_OK;
   dim3 grid((unsigned)((nslices + 7) / 8), (unsigned)B);
   VQK_DISPATCH_DTYPE(dtype, (k_slice_pass<T><<<grid, 256, 0, st>>>((const T*)logits, ld, V, sp, slice_max, part_score,
-                                                                   part_token, nslices)));
+                                                                   part_token, nslices, lp_max, lp_sum)));
+  VQK_LAUNCH_CHECK();
+  return VQK_OK;
+}
+
+int launch_logprob(const void* logits, int dtype, long long ld, int B, int V, const float* lp_max, const float* lp_sum,
+                   int nslices, const long long* tokens, float* logprobs, cudaStream_t st) {
+  if (B == 0 || V == 0) return VQK_OK;
+  VQK_DISPATCH_DTYPE(dtype, (k_logprob<T><<<(unsigned)B, 32, 0, st>>>((const T*)logits, ld, V, lp_max, lp_sum, nslices, tokens,
+                                                                      logprobs)));
   VQK_LAUNCH_CHECK();
   return VQK_OK;
 }

@@ -162,6 +162,7 @@ struct SampleDev {  // vqk_sample_params with device pointers, passed by value
   const float* thr;
   long long vocab_offset;
   long long vocab_total;
+  float* logprobs;  // optional out [B]: raw log-softmax of the sampled token (stand-alone sampler)
 };
 
 __device__ __forceinline__ RowMeta decode_row(const SampleDev& sp, int b) {

@@ -49,6 +49,7 @@ class SampleParams(ctypes.Structure):
     _fields_ = [
         ("temperature", c_void_p), ("seeds", c_void_p), ("top_k", c_void_p), ("top_p", c_void_p),
         ("topk_threshold", c_void_p), ("vocab_offset", c_int64), ("vocab_total", c_int64),
+        ("logprobs", c_void_p),
     ]
 
 

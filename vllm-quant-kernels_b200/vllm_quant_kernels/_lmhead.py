@@ -388,9 +388,12 @@ class LMHeadShard:
 # stand-alone sampler entry points
 # --------------------------------------------------------------------------
 
-def sample_logits(logits: torch.Tensor, sp: SamplingArgs, records: bool = False):
+def sample_logits(logits: torch.Tensor, sp: SamplingArgs, records: bool = False, return_logprobs: bool = False):
     """Sampler on materialised logits [B, V] (fp32 / bf16 / fp16).  Returns
-    (tokens int64, scores fp32), or the uint8 [B, 1024] shard records if `records`."""
+    (tokens int64, scores fp32), or the uint8 [B, 1024] shard records if `records`.
+    `return_logprobs`: also the fp32 raw log-softmax of every sampled token (of the logits as
+    given, before temperature / top-k / top-p: vLLM's default "raw_logprobs"), computed from the
+    first pass's per-slice maxima and sums of exponentials; single shard only."""
     _require_cuda(logits, "logits")
     assert logits.dim() == 2 and logits.dtype in _DT
     if logits.stride(1) != 1:
@@ -403,17 +406,24 @@ def sample_logits(logits: torch.Tensor, sp: SamplingArgs, records: bool = False)
         _ffi.check(n)
     ws = _WS.get(dev, n)
     spc = sp.to_c(B, V)
-    tokens = scores = rec = None
+    tokens = scores = rec = lps = None
     if records:
+        if return_logprobs:
+            raise ValueError("log-probabilities belong to the merged token: not with shard records")
         rec = torch.empty(B, _ffi.RECORD_BYTES, dtype=torch.uint8, device=dev)
     else:
         tokens = torch.empty(B, dtype=torch.int64, device=dev)
         scores = torch.empty(B, dtype=torch.float32, device=dev)
+    if return_logprobs:
+        lps = torch.empty(B, dtype=torch.float32, device=dev)
+        spc.logprobs = lps.data_ptr()
     if B:
         with torch.cuda.device(dev):
             _ffi.check(L.vqk_sample(logits.data_ptr(), _DT[logits.dtype], B, V, logits.stride(0), ctypes.byref(spc),
                                     _ptr(tokens), _ptr(scores), _ptr(rec), ws.data_ptr(), n, _stream(logits)))
-    return rec if records else (tokens, scores)
+    if records:
+        return rec
+    return (tokens, scores, lps) if return_logprobs else (tokens, scores)
 
 
 def finalize_records(gathered: torch.Tensor, sp: SamplingArgs):
