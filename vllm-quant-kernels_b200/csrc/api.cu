@@ -424,7 +424,10 @@ static int lm_head_forward_impl(vqk_lm_head* h, const void* x, int x_dtype, int6
   s.single_shard = (tokens && !peer) ? 1 : 0;
   s.row_flag = fuse_tail ? ws.row_flag : nullptr;
   s.peer = pt;
-  return launch_select(s, st);
+  // behind the streaming kernel as its programmatic dependent: its CTAs are in place when that kernel ends (1.8 us
+  // per step; behind the tensor-core kernels the same cost the MXFP4 step 4 - 7 us, so there it is launched
+  // the plain way).  An event record in between would separate the two.
+  return launch_select(s, st, !use_umma && pdl_enabled() && !h->ev_stop);
 }
 
 extern "C" int vqk_lm_head_forward(vqk_lm_head* h, const void* x, int x_dtype, int64_t B, int64_t ldx,

@@ -145,7 +145,9 @@ int launch_logprob(const void* logits, int dtype, long long ld, int B, int V, co
 inline int slice_pass_nslices(long long V) { return (int)((V + 255) / 256); }
 // cluster-per-row selection: tau from slice maxima, candidate collection, final choice / record;
 // rows that do not fit the candidate scheme are resolved by an exact full-row pass inside
-int launch_select(const SelectParams& p, cudaStream_t st);
+// `after_lm_head`: launched as a programmatic dependent of the lm_head kernel before it on the stream (its CTAs are
+// in place, waiting, when that kernel ends)
+int launch_select(const SelectParams& p, cudaStream_t st, bool after_lm_head = false);
 // merge gathered records
 int launch_finalize(const uint8_t* records, int G, int B, const SampleDev& sp, long long* tokens, float* scores,
                     cudaStream_t st);

@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   volatile int* seq_tag = reinterpret_cast<volatile int*>(freeb + 2 * kGroups + 1);  // [group][4]: 2 m = tile m is being fetched, 2 m + 1 = seq_val holds it
   volatile int* seq_val = seq_tag + kGroups * 4;                                       // [group][4]
 
+  pdl_launch_dependents();  // the full-row sampler kernel behind this one may take its place as SMs come free
   dbg_stamp(p, 0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = warp >> 2, wq = warp & 3;

@@ -435,6 +435,7 @@ __global__ void __launch_bounds__(kSelThreads) k_select(const SelectParams p) {
   const int crank = (int)cluster.block_rank();
   const int csize = (int)cluster.num_blocks();  // 1, 2, 4 or 8: chosen by the launcher from the row length
   const int b = blockIdx.y, tid = threadIdx.x;
+  pdl_wait();  // launched behind an lm_head kernel as its programmatic dependent: everything read below is that kernel's
   // rows the lm_head kernel's own tail already resolved (uniform over the cluster: no barrier is reached)
   if (p.row_flag && p.row_flag[b] == 0) return;
   const RowMeta m = decode_row(p.sp, b);
@@ -740,7 +741,7 @@ int launch_logprob(const void* logits, int dtype, long long ld, int B, int V, co
   return VQK_OK;
 }
 
-int launch_select(const SelectParams& p, cudaStream_t st) {
+int launch_select(const SelectParams& p, cudaStream_t st, bool after_lm_head) {
   if (p.B == 0) return VQK_OK;
   // CTAs per row: enough that a CTA's share fits the registers it preloads (kSelShare bytes),
   // at most kClusterSize; short rows (a vocab shard) take one CTA and
@@ -760,13 +761,15 @@ int launch_select(const SelectParams& p, cudaStream_t st) {
   cfg.blockDim = dim3(narrow ? 512 : 1024);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)cs;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = after_lm_head ? 2 : 1;
   cudaError_t le = cudaSuccess;
   if (narrow) {
     VQK_DISPATCH_DTYPE(p.dtype, (le = cudaLaunchKernelEx(&cfg, k_select<T, 512>, p)));
