@@ -91,8 +91,10 @@ __device__ inline PeerRowResult peer_exchange_row(const PeerTable& pt, int b, fl
   int tk = 0x7fffffff;
   if (lane < G) {
     const unsigned long long* slot = mine + ((parity_off + lane) * pt.max_rows + b) * kWireWords;
-    const unsigned long long w0 = peer_wait_word(slot, pt.wait_polls);
-    const unsigned long long w1 = w0 ? peer_wait_word(slot + 1, pt.wait_polls) : 0ull;
+    // both header words in flight at once; the bounded wait only for what has not landed yet
+    unsigned long long w0 = ld_sys_u64(slot), w1 = ld_sys_u64(slot + 1);
+    if (!w0) w0 = peer_wait_word(slot, pt.wait_polls);
+    if (w0 && !w1) w1 = peer_wait_word(slot + 1, pt.wait_polls);
     if (!w0 || !w1) late = 1;
     else {
       const unsigned int hi = (unsigned int)(w0 >> 32);
@@ -131,16 +133,32 @@ __device__ inline PeerRowResult peer_exchange_row(const PeerTable& pt, int b, fl
     r.best_t = __shfl_sync(0xffffffffu, t, 0);
   }
   // ---- candidates of every rank ----------------------------------------------------------------------
-  for (int g = 0; g < G; ++g) {
-    const int cnt = __shfl_sync(0xffffffffu, ng, g);
-    const int base = __shfl_sync(0xffffffffu, incl - ng, g);
-    const unsigned long long* slot = mine + ((parity_off + g) * pt.max_rows + b) * kWireWords + 2;
-    for (int i = lane; i < cnt; i += 32) {
-      const unsigned long long w = peer_wait_word(slot + i, pt.wait_polls);
-      if (!w) late = 1;
-      else if (!r.bad) {
-        mv[base + i] = __uint_as_float((unsigned int)w);
-        mt[base + i] = (int)((unsigned int)(w >> 32) & 0x7fffffffu);
+  // A lane takes words lane, lane + 32, ... of every rank's list.  A rank's four loads are put in flight
+  // together (each is an L2 round trip for this lone warp; one after the other they cost 0.7 us
+  // apiece, 11 us at eight ranks); the bounded wait is only for words that have not landed yet.
+  constexpr int kPer = (VQK_RECORD_CAP + 31) / 32;  // words per lane and rank at most
+  constexpr int kFly = 4;                           // loads in flight together (a rank's worth)
+  for (int t0 = 0; t0 < G * kPer; t0 += kFly) {
+    unsigned long long w[kFly];
+#pragma unroll
+    for (int u = 0; u < kFly; ++u) {
+      const int t = t0 + u, g = t / kPer, i = lane + 32 * (t % kPer);
+      const int cnt = __shfl_sync(0xffffffffu, ng, g & 31);
+      w[u] = 1ull;
+      if (g < G && i < cnt) w[u] = ld_sys_u64(mine + ((parity_off + g) * pt.max_rows + b) * kWireWords + 2 + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kFly; ++u) {
+      const int t = t0 + u, g = t / kPer, i = lane + 32 * (t % kPer);
+      const int cnt = __shfl_sync(0xffffffffu, ng, g & 31);
+      const int base = __shfl_sync(0xffffffffu, incl - ng, g & 31);
+      if (g < G && i < cnt) {
+        if (!w[u]) w[u] = peer_wait_word(mine + ((parity_off + g) * pt.max_rows + b) * kWireWords + 2 + i, pt.wait_polls);
+        if (!w[u]) late = 1;
+        else if (!r.bad) {
+          mv[base + i] = __uint_as_float((unsigned int)w[u]);
+          mt[base + i] = (int)((unsigned int)(w[u] >> 32) & 0x7fffffffu);
+        }
       }
     }
   }
