@@ -88,3 +88,42 @@ def test_static_scratch_sampler_rejects_sizes_beyond_its_maximum():
     assert L.vqk_sample_static(256, _ffi.F32, 1, _ffi.STATIC_MAX_VOCAB + 1, _ffi.STATIC_MAX_VOCAB + 1,
                                ctypes.byref(sp), 256, None, None) == -7
     assert b"vqk_sample_static" in L.vqk_strerror(-7)
+
+
+def test_static_scratch_sampler_inside_a_cuda_graph():
+    """The use the entry point is made for: after one warm-up call it is captured into a CUDA
+    graph (nothing may be allocated between the begin and end of a capture) with caller-owned
+    outputs, and every replay gives what the workspace-based sampler gives."""
+    from vllm_quant_kernels import _ffi
+    L = _ffi.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, V = 6, 151936
+    logits, a = _case(B, V, 21, torch.bfloat16, dev)
+    sp = _params(_ffi, B, V, a)
+    n = L.vqk_sample_workspace_bytes(B, V)
+    ws = torch.empty(n, dtype=torch.uint8, device=dev)
+    tok_ref = torch.empty(B, dtype=torch.int64, device=dev)
+    sc_ref = torch.empty(B, dtype=torch.float32, device=dev)
+    assert L.vqk_sample(logits.data_ptr(), _ffi.BF16, B, V, logits.stride(0), ctypes.byref(sp), tok_ref.data_ptr(),
+                        sc_ref.data_ptr(), None, ws.data_ptr(), n, torch.cuda.current_stream().cuda_stream) == 0
+    tok = torch.full((B,), -9, dtype=torch.int64, device=dev)
+    sc = torch.zeros(B, dtype=torch.float32, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        assert L.vqk_sample_static(logits.data_ptr(), _ffi.BF16, B, V, logits.stride(0), ctypes.byref(sp), tok.data_ptr(),
+                                   sc.data_ptr(), side.cuda_stream) == 0          # warm-up: looks the scratch up
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            rc = L.vqk_sample_static(logits.data_ptr(), _ffi.BF16, B, V, logits.stride(0), ctypes.byref(sp),
+                                     tok.data_ptr(), sc.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        for _ in range(2):
+            tok.fill_(-9)
+            sc.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(tok, tok_ref) and torch.equal(sc, sc_ref)
+    torch.cuda.current_stream().wait_stream(side)
