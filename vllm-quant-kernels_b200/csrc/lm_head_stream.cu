@@ -369,11 +369,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_lm_head_stream(const LmHeadPara
   };
   auto tile_of = [&](int m, int prev) -> int {  // the group's m-th tile (m >= 1), `prev` its (m - 1)-th
     if (!dynamic || m < 2) return prev + tstride;
-    int v = main_end;  // nothing: when the wait runs out the warp stops taking tiles
+    int v = -1;
     if (lane == 0) {
       for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (gtag[m & 3] == 2 * m + 1) { v = gval[m & 3]; break; }
         if ((it & 255u) == 255u && *abort_flag) break;
+      }
+      if (v < 0) {  // the wait ran out (it never should): flag the launch as failed and stop taking tiles
+        *abort_flag = 1;
+        atomicExch(&g_stream_error, 1);
+        v = main_end;
       }
     }
     return __shfl_sync(0xffffffffu, v, 0);
