@@ -14,6 +14,10 @@
 // tile) the W8A16 kernel ran 9 % slower; epilogue warps of their own (20 warps, 96 registers)
 // could not keep up beyond four batch columns.  A warp keeps ONE set of weight registers and
 // refills it unit by unit instead of double-buffering whole batches.
+// Tiles: a group's first two are the static round-robin ones, the rest come from a per-launch
+// counter (the CTAs stream at different rates); the leftover tiles, fewer than groups, are taken one
+// per CTA with K split over all sixteen warps.  At its end every CTA merges its groups' sampler
+// state into one record per batch row, and the last CTA to finish runs the sampler tail (tail.cuh).
 //
 // Replaces int8_gmv / int8_gemm / fp8_gemm / int8_w8a8_gemm / mxfp8_gemm / mxfp4_gemm of the
 // reference (src/vllm_quant_kernels/_kernels.py) for batch <= 32.

@@ -1,6 +1,6 @@
-// Sampler tail of the decode-sized lm_head kernels: one CTA of the grid turns the per-slice results
-// every CTA left in memory into the step's tokens, one warp per batch row, while those results are
-// still in L2.
+// Sampler tail of the streaming lm_head kernel at decode sizes: one CTA of the grid turns the
+// records every CTA left in memory into the step's tokens, one warp per batch row, while those
+// records are still in L2.
 //
 // Per batch row every CTA leaves one 64-byte record (CtaList, lm_head.cuh):
 //   * the Gumbel (or greedy) winner of the CTA's vocab rows, for rows without top-k / top-p;
